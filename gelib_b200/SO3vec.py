@@ -1,0 +1,255 @@
+"""``gelib.SO3vec`` / ``gelib.SO3vecArr`` and their autograd functions on the B200 kernels.
+
+Mirrors python/src/gelib/SO3vec.py and python/src/gelib/SO3vecArr.py of GElib (constructors, accessors,
+``CGproduct`` / ``DiagCGproduct`` with ``maxl`` truncation, ``odot``, ``apply``, ``*`` with SO3weights,
+same autograd Function names).  The whole product -- every (l1,l2)->l triple -- is one kernel launch
+forward and one backward instead of one launch per triple (core/Gvec.hpp:311-389).
+"""
+import torch
+
+from . import backend as gb
+from .gelib_common import common_batch
+from .SO3part import SO3part, SO3partArr
+
+
+def _vec_forward(ctx, k1, k2, maxl, args, diag, part_cls):
+    ctx.k1, ctx.k2, ctx.diag = k1, k2, diag
+    ctx.save_for_backward(*args)
+    xs, ys = [a.detach() for a in args[0:k1]], [a.detach() for a in args[k1:k1 + k2]]
+    x, y = gb.SO3vec.view(xs), gb.SO3vec.view(ys)
+    b = common_batch(xs[0], ys[0])
+    tau = x.get_tau().DiagCGproduct(y.get_tau(), maxl) if diag else x.get_tau().CGproduct(y.get_tau(), maxl)
+    big = xs[0] if xs[0].dim() >= ys[0].dim() else ys[0]
+    grid = list(big.shape[1:-2])
+    rparts = [torch.empty([b] + grid + [2 * l + 1, n], dtype=torch.complex64, device=xs[0].device)
+              for l, n in tau.get_parts().items()]
+    r = gb.SO3vec.view(rparts)
+    if diag:
+        r.addDiagCGproduct(x, y, overwrite=True)
+    else:
+        r.addCGproduct(x, y, overwrite=True)
+    return tuple(p.as_subclass(part_cls) for p in rparts)
+
+
+def _vec_backward(ctx, gargs):
+    k1, k2 = ctx.k1, ctx.k2
+    saved = ctx.saved_tensors
+    grads = [torch.zeros_like(t) for t in saved]
+    x, y = gb.SO3vec.view(list(saved[0:k1])), gb.SO3vec.view(list(saved[k1:k1 + k2]))
+    g = gb.SO3vec.view([a.as_subclass(torch.Tensor) for a in gargs])
+    xg, yg = gb.SO3vec.view(grads[0:k1]), gb.SO3vec.view(grads[k1:k1 + k2])
+    if ctx.diag:
+        gb.SO3vec.addDiagCGproduct_back01(xg, yg, g, x, y)
+    else:
+        gb.SO3vec.addCGproduct_back01(xg, yg, g, x, y)
+    return tuple([None, None, None] + grads)
+
+
+class SO3vec_CGproductFn(torch.autograd.Function):
+    """python/src/gelib/SO3vec.py:233-270."""
+
+    @staticmethod
+    def forward(ctx, k1, k2, maxl, *args):
+        return _vec_forward(ctx, k1, k2, maxl, args, False, SO3part)
+
+    @staticmethod
+    def backward(ctx, *args):
+        return _vec_backward(ctx, args)
+
+
+class SO3vec_DiagCGproductFn(torch.autograd.Function):
+    """python/src/gelib/SO3vec.py:273-309."""
+
+    @staticmethod
+    def forward(ctx, k1, k2, maxl, *args):
+        return _vec_forward(ctx, k1, k2, maxl, args, True, SO3part)
+
+    @staticmethod
+    def backward(ctx, *args):
+        return _vec_backward(ctx, args)
+
+
+class SO3vecArr_CGproductFn(torch.autograd.Function):
+    """python/src/gelib/SO3vecArr.py:324-361."""
+
+    @staticmethod
+    def forward(ctx, k1, k2, maxl, *args):
+        return _vec_forward(ctx, k1, k2, maxl, args, False, SO3partArr)
+
+    @staticmethod
+    def backward(ctx, *args):
+        return _vec_backward(ctx, args)
+
+
+class SO3vecArr_DiagCGproductFn(torch.autograd.Function):
+    """python/src/gelib/SO3vecArr.py:364-401 (which drops maxl; here maxl is honoured as for SO3vec)."""
+
+    @staticmethod
+    def forward(ctx, k1, k2, maxl, *args):
+        return _vec_forward(ctx, k1, k2, maxl, args, True, SO3partArr)
+
+    @staticmethod
+    def backward(ctx, *args):
+        return _vec_backward(ctx, args)
+
+
+class _VecBase:
+    """What SO3vec and SO3vecArr share: a dict l -> part tensor."""
+    _part = SO3part
+    _cg_fn = SO3vec_CGproductFn
+    _diag_fn = SO3vec_DiagCGproductFn
+
+    def __init__(self, *args):
+        self.parts = {}
+        for x in args:
+            assert isinstance(x, torch.Tensor)
+            self.parts[(x.size(-2) - 1) // 2] = x
+
+    @classmethod
+    def zeros_like(cls, x):
+        R = cls()
+        for l, p in x.parts.items():
+            R.parts[l] = cls._part(torch.zeros_like(p))
+        return R
+
+    @classmethod
+    def randn_like(cls, x):
+        R = cls()
+        for l, p in x.parts.items():
+            R.parts[l] = cls._part(torch.randn_like(p))
+        return R
+
+    def backend(self):
+        return gb.SO3vec.view(self.parts)
+
+    def getb(self):
+        return self.parts[min(self.parts)].size(0)
+
+    def tau(self):
+        return {l: p.size(-1) for l, p in self.parts.items()}
+
+    get_type = tau
+
+    def l_max(self):
+        return max(self.parts)
+
+    def requires_grad_(self):
+        for p in self.parts.values():
+            p.requires_grad_()
+
+    def get_grad(self):
+        return type(self)(*[p.grad for p in self.parts.values()])
+
+    def apply(self, R):
+        r = type(self)()
+        for l, p in self.parts.items():
+            r.parts[l] = self._part(p).apply(R)
+        return r
+
+    def odot(self, y):
+        assert list(self.parts.keys()) == list(y.parts.keys())
+        return sum(self._part(self.parts[l]).odot(y.parts[l]) for l in self.parts)
+
+    def __add__(self, y):
+        assert list(self.parts.keys()) == list(y.parts.keys())
+        return type(self)(*[self.parts[l] + y.parts[l] for l in self.parts])
+
+    def __mul__(self, w):
+        """Channel mixing with SO3weights: part l times the l-th weight matrix (python/src/gelib/SO3vec.py:174-177)."""
+        return type(self)(*[torch.matmul(p, m) for p, m in zip(self.parts.values(), w.parts)])
+
+    def to(self, device):
+        return type(self)(*[p.to(device) for p in self.parts.values()])
+
+    def CGproduct(self, y, maxl=-1):
+        """Full Clebsch-Gordan product: all (l1,l2)->l with l <= maxl, blocks ordered by (l1, l2)."""
+        xp, yp = list(self.parts.values()), list(y.parts.values())
+        return type(self)(*self._cg_fn.apply(len(xp), len(yp), maxl, *(xp + yp)))
+
+    def DiagCGproduct(self, y, maxl=-1):
+        xp, yp = list(self.parts.values()), list(y.parts.values())
+        return type(self)(*self._diag_fn.apply(len(xp), len(yp), maxl, *(xp + yp)))
+
+    def __repr__(self):
+        return "<GElib::%s of type %s [b=%d]>" % (type(self).__name__, self.tau(), self.getb())
+
+    def __str__(self):
+        return "\n".join("Part l=%d:\n%s\n" % (l, p.as_subclass(torch.Tensor)) for l, p in self.parts.items())
+
+
+class SO3vec(_VecBase):
+    """An SO(3)-covariant vector: a sequence of SO3parts keyed by l."""
+
+    @classmethod
+    def zeros(cls, b, tau, device='cpu'):
+        R = SO3vec()
+        for l, n in tau.items():
+            R.parts[l] = SO3part.zeros(b, l, n, device=device)
+        return R
+
+    @classmethod
+    def randn(cls, b, tau, device='cpu'):
+        R = SO3vec()
+        for l, n in tau.items():
+            R.parts[l] = SO3part.randn(b, l, n, device=device)
+        return R
+
+    @classmethod
+    def Fzeros(cls, b, maxl, device='cpu'):
+        return SO3vec(*[SO3part.Fzeros(b, l, device) for l in range(maxl + 1)])
+
+    @classmethod
+    def Frandn(cls, b, maxl, device='cpu'):
+        return SO3vec(*[SO3part.Frandn(b, l, device) for l in range(maxl + 1)])
+
+    @classmethod
+    def spharm(cls, l, X):
+        """The SO3vec whose only part is Y_l(X), X (b, 3, n) float32."""
+        assert X.dim() == 3
+        return SO3vec(SO3part.spharm(l, X))
+
+    @classmethod
+    def spharms(cls, maxl, X):
+        """Parts l = 0..maxl of the spherical harmonics of X from one pass over the points."""
+        assert X.dim() == 3
+        parts = [torch.empty([X.size(0), 2 * l + 1, X.size(2)], dtype=torch.complex64, device=X.device)
+                 for l in range(maxl + 1)]
+        gb.SO3vec.view(parts).add_spharm(X, overwrite=True)
+        return SO3vec(*[SO3part(p) for p in parts])
+
+
+class SO3vecArr(_VecBase):
+    """An array of SO3vecs: parts are (b, a1..ak, 2l+1, n)."""
+    _part = SO3partArr
+    _cg_fn = SO3vecArr_CGproductFn
+    _diag_fn = SO3vecArr_DiagCGproductFn
+
+    @classmethod
+    def zeros(cls, b, adims, tau, device='cpu'):
+        return SO3vecArr(*[SO3partArr.zeros(b, adims, l, n, device) for l, n in tau.items()])
+
+    @classmethod
+    def ones(cls, b, adims, tau, device='cpu'):
+        return SO3vecArr(*[SO3partArr.ones(b, adims, l, n, device) for l, n in tau.items()])
+
+    @classmethod
+    def randn(cls, b, adims, tau, device='cpu'):
+        return SO3vecArr(*[SO3partArr.randn(b, adims, l, n, device) for l, n in tau.items()])
+
+    @classmethod
+    def spharm(cls, l, X):
+        return SO3vecArr(SO3partArr.spharm(l, X))
+
+    def get_adims(self):
+        p = self.parts[min(self.parts)]
+        return list(p.size()[1:p.dim() - 2])
+
+
+def MakeZeroSO3parts(b, tau, device):
+    """python/src/gelib/SO3vec.py:531-536."""
+    return [SO3part.zeros(b, l, n, device) for l, n in tau.items()]
+
+
+def MakeZeroSO3partArrs(b, adims, tau, device):
+    """python/src/gelib/SO3vecArr.py:584-588."""
+    return [SO3partArr.zeros(b, adims, l, n, device) for l, n in tau.items()]

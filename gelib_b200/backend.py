@@ -1,0 +1,246 @@
+"""Stand-in for GElib's pybind11 module ``gelib_base`` on the Clebsch-Gordan path.
+
+Same class and method names, argument order and defaults as the reference bindings
+(python/bindings/SO3part_py.cpp:15-58, python/bindings/SO3vec_py.cpp:15-59,
+python/bindings/SO3type_py.cpp:16-43 of GElib); the objects are zero-copy views of torch tensors and
+every method forwards to one C-ABI call of ``libgelib_b200.so``.  Additions over the reference are
+keyword-only or new names: ``overwrite=`` on the forward products, the fused ``*_back01`` gradients and
+``SO3vec.add_spharm``.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import GELIB_OVERWRITE, check, descriptor, descriptor_array, device_guard, lib, stream_of
+
+
+def _ints(v):
+    return (ctypes.c_int * max(1, len(v)))(*v)
+
+
+class SO3type:
+    """The type of an SO3vec: l -> number of channels.  python/bindings/SO3type_py.cpp:16-43."""
+
+    def __init__(self, arg=None):
+        self.parts = {}
+        if isinstance(arg, dict):
+            self.parts = {int(l): int(n) for l, n in sorted(arg.items())}
+        elif arg is not None:
+            self.parts = {l: int(n) for l, n in enumerate(arg)}
+
+    def __len__(self):
+        return len(self.parts)
+
+    def maxl(self):
+        return max(self.parts) if self.parts else -1
+
+    def __getitem__(self, l):
+        return self.parts.get(l, 0)
+
+    def __setitem__(self, l, n):
+        self.parts[l] = n
+        self.parts = dict(sorted(self.parts.items()))
+
+    def get_parts(self):
+        return dict(self.parts)
+
+    def _product(self, y, maxl, diag):
+        xl, xn = list(self.parts.keys()), list(self.parts.values())
+        yl, yn = list(y.parts.keys()), list(y.parts.values())
+        cap = (max(xl) + max(yl) + 1) if xl and yl else 1
+        ol, on = (ctypes.c_int * cap)(), (ctypes.c_int * cap)()
+        k = lib().gelib_SO3type_CGproduct(len(xl), _ints(xl), _ints(xn), len(yl), _ints(yl), _ints(yn), maxl,
+                                          1 if diag else 0, cap, ol, on)
+        if k < 0:
+            raise RuntimeError("GElib error: product type does not fit")
+        return SO3type({ol[i]: on[i] for i in range(k)})
+
+    def CGproduct(self, y, maxl=-1):
+        return self._product(y, maxl, False)
+
+    def DiagCGproduct(self, y, maxl=-1):
+        return self._product(y, maxl, True)
+
+    def __eq__(self, other):
+        return isinstance(other, SO3type) and self.parts == other.parts
+
+    def str(self, indent=""):
+        return indent + "(" + ",".join("%d:%d" % (l, n) for l, n in self.parts.items()) + ")"
+
+    __str__ = str
+
+    def __repr__(self):
+        return "<GElib::SO3type" + self.str() + ">"
+
+
+def CGproduct(x, y, maxl=-1):
+    """``gelib_base.CGproduct`` on two SO3types (python/bindings/SO3type_py.cpp:39-43)."""
+    return x.CGproduct(y, maxl)
+
+
+class SO3part:
+    """Zero-copy view of a complex64 tensor (batch, [grid...], 2l+1, channels)."""
+
+    def __init__(self, t):
+        self.t = t
+
+    @staticmethod
+    def view(t):
+        return SO3part(t)
+
+    def getl(self):
+        return (self.t.size(-2) - 1) // 2
+
+    def getn(self):
+        return self.t.size(-1)
+
+    def _call3(self, name, a, b, c, offs, flags=0):
+        with device_guard(a):
+            da, db, dc = descriptor(a), descriptor(b), descriptor(c)
+            return check(getattr(lib(), name)(ctypes.byref(da), ctypes.byref(db), ctypes.byref(dc), offs, flags,
+                                              stream_of(a)))
+
+    def add_CGproduct(self, x, y, offs=0, *, overwrite=False):
+        self._call3("gelib_SO3part_addCGproduct", self.t, x.t, y.t, offs, GELIB_OVERWRITE if overwrite else 0)
+
+    def add_CGproduct_back0(self, g, y, offs=0):
+        self._call3("gelib_SO3part_addCGproduct_back0", self.t, g.t, y.t, offs)
+
+    def add_CGproduct_back1(self, g, x, offs=0):
+        self._call3("gelib_SO3part_addCGproduct_back1", self.t, g.t, x.t, offs)
+
+    def add_DiagCGproduct(self, x, y, offs=0, *, overwrite=False):
+        self._call3("gelib_SO3part_addDiagCGproduct", self.t, x.t, y.t, offs, GELIB_OVERWRITE if overwrite else 0)
+
+    def add_DiagCGproduct_back0(self, g, y, offs=0):
+        self._call3("gelib_SO3part_addDiagCGproduct_back0", self.t, g.t, y.t, offs)
+
+    def add_DiagCGproduct_back1(self, g, x, offs=0):
+        self._call3("gelib_SO3part_addDiagCGproduct_back1", self.t, g.t, x.t, offs)
+
+    @staticmethod
+    def _back01(name, xg, yg, g, x, y, offs):
+        with device_guard(g.t):
+            d = [descriptor(v.t) for v in (xg, yg, g, x, y)]
+            return check(getattr(lib(), name)(*[ctypes.byref(v) for v in d], offs, 0, stream_of(g.t)))
+
+    @staticmethod
+    def add_CGproduct_back01(xg, yg, g, x, y, offs=0):
+        """Both gradients from one pass over g (fused back0 + back1)."""
+        SO3part._back01("gelib_SO3part_addCGproduct_back01", xg, yg, g, x, y, offs)
+
+    @staticmethod
+    def add_DiagCGproduct_back01(xg, yg, g, x, y, offs=0):
+        SO3part._back01("gelib_SO3part_addDiagCGproduct_back01", xg, yg, g, x, y, offs)
+
+    def add_spharm(self, X, *, overwrite=False):
+        """self += Y_l(X) for X (batch, [grid...], 3, channels) float32, or (3, channels) broadcast over the batch."""
+        if X.dim() == 2:
+            X = X.unsqueeze(0)
+        with device_guard(self.t):
+            dr, dx = descriptor(self.t), descriptor(X, real=True)
+            check(lib().gelib_SO3part_addSPharm(ctypes.byref(dr), ctypes.byref(dx), GELIB_OVERWRITE if overwrite else 0,
+                                                stream_of(self.t)))
+
+    def __repr__(self):
+        return "<GElib::SO3part(l=%d,n=%d)>" % (self.getl(), self.getn())
+
+    def str(self, indent=""):
+        return indent + str(self.t)
+
+    __str__ = str
+
+
+class SO3vec:
+    """Zero-copy view of a list (l read from the shapes) or dict l -> tensor of SO3parts."""
+
+    def __init__(self, parts):
+        self.parts = parts  # dict l -> tensor, ascending l
+
+    @staticmethod
+    def view(parts):
+        if isinstance(parts, dict):
+            return SO3vec(dict(sorted((int(l), t) for l, t in parts.items())))
+        return SO3vec(dict(sorted(((t.size(-2) - 1) // 2, t) for t in parts)))
+
+    def get_tau(self):
+        return SO3type({l: t.size(-1) for l, t in self.parts.items()})
+
+    def _tensors(self):
+        return list(self.parts.values())
+
+    def _call3(self, name, a, b, c, flags=0):
+        ta, tb, tc = a._tensors(), b._tensors(), c._tensors()
+        if not ta or not tb or not tc:
+            return True
+        with device_guard(ta[0]):
+            return check(getattr(lib(), name)(len(ta), descriptor_array(ta), len(tb), descriptor_array(tb), len(tc),
+                                              descriptor_array(tc), flags, stream_of(ta[0])))
+
+    def addCGproduct(self, x, y, *, overwrite=False):
+        self._call3("gelib_SO3vec_addCGproduct", self, x, y, GELIB_OVERWRITE if overwrite else 0)
+
+    def addCGproduct_back0(self, g, y):
+        self._call3("gelib_SO3vec_addCGproduct_back0", self, g, y)
+
+    def addCGproduct_back1(self, g, x):
+        self._call3("gelib_SO3vec_addCGproduct_back1", self, g, x)
+
+    def addDiagCGproduct(self, x, y, *, overwrite=False):
+        self._call3("gelib_SO3vec_addDiagCGproduct", self, x, y, GELIB_OVERWRITE if overwrite else 0)
+
+    def addDiagCGproduct_back0(self, g, y):
+        self._call3("gelib_SO3vec_addDiagCGproduct_back0", self, g, y)
+
+    def addDiagCGproduct_back1(self, g, x):
+        self._call3("gelib_SO3vec_addDiagCGproduct_back1", self, g, x)
+
+    @staticmethod
+    def _back01(name, xg, yg, g, x, y):
+        txg, tyg, tg, tx, ty = (v._tensors() for v in (xg, yg, g, x, y))
+        if not tg or not tx or not ty:
+            return True
+        with device_guard(tg[0]):
+            return check(getattr(lib(), name)(len(txg), descriptor_array(txg), len(tyg), descriptor_array(tyg),
+                                              len(tg), descriptor_array(tg), descriptor_array(tx),
+                                              descriptor_array(ty), 0, stream_of(tg[0])))
+
+    @staticmethod
+    def addCGproduct_back01(xg, yg, g, x, y):
+        """Both gradients of the full product from one pass over g."""
+        SO3vec._back01("gelib_SO3vec_addCGproduct_back01", xg, yg, g, x, y)
+
+    @staticmethod
+    def addDiagCGproduct_back01(xg, yg, g, x, y):
+        SO3vec._back01("gelib_SO3vec_addDiagCGproduct_back01", xg, yg, g, x, y)
+
+    def add_spharm(self, X, *, overwrite=False):
+        """Every part += its spherical harmonics of X, from one Legendre recursion per point."""
+        tr = self._tensors()
+        if X.dim() == 2:
+            X = X.unsqueeze(0)
+        with device_guard(tr[0]):
+            dx = descriptor(X, real=True)
+            check(lib().gelib_SO3vec_addSPharm(len(tr), descriptor_array(tr), ctypes.byref(dx),
+                                               GELIB_OVERWRITE if overwrite else 0, stream_of(tr[0])))
+
+    def __repr__(self):
+        return "<GElib::SO3vec of type " + self.get_tau().str() + ">"
+
+    def str(self, indent=""):
+        return "\n".join("%sPart l=%d:\n%s\n" % (indent, l, t) for l, t in self.parts.items())
+
+    __str__ = str
+
+
+def SO3CGmatrix(l1, l2, l):
+    """Dense (2l1+1) x (2l2+1) coefficient matrix (``gelib.SO3CGmatrix`` of the docs, python/docs/source/SO3CG.rst:49-53)."""
+    out = torch.zeros(2 * l1 + 1, 2 * l2 + 1, dtype=torch.float32)
+    if lib().gelib_CGmatrix(l1, l2, l, out.data_ptr()) != _lib.GELIB_OK:
+        raise RuntimeError(_lib.last_error())
+    return out
+
+
+def kernel_launch_count():
+    return int(lib().gelib_kernel_launch_count())

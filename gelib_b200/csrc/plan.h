@@ -1,0 +1,41 @@
+// Host-side description of one product call and the per-device plan cache.
+#pragma once
+#include <functional>
+#include <vector>
+
+#include "common.h"
+
+namespace gelib_b200 {
+
+// A validated vector-level product.  For the forward pass `r` is the output; for the backward
+// passes `r` holds the upstream gradient g and xg / yg the requested outputs (either may be empty).
+struct VecCall {
+  std::vector<PartView> x, y, r, xg, yg;
+  CellGrid cg;
+  bool diag = false;
+  int offs_extra = 0;    // added to every triple's channel offset (the `offs` of the SO3part-level calls)
+  int flags = 0;
+  bool r_bcast = false;  // an output tensor is broadcast over cells: results must be summed (atomics)
+  bool xg_bcast = false, yg_bcast = false;
+  bool dense_channels = true;  // every tensor has channel stride 2 floats
+  bool vec_ok = true;          // 16-byte alignment of bases/strides/offsets holds for float4 access
+};
+
+std::vector<PartSig> sig_of(const std::vector<PartView>& v);
+
+// Returns the cached plan for `key` on the current device, building and uploading it on first use.
+// `build` fills sched / h_items / h_jobs.  nullptr (with the error message set) on CUDA failure.
+DevicePlan* get_plan(const std::vector<int>& key, const std::function<void(DevicePlan&)>& build);
+
+// Kernel families (each returns a status code).
+int launch_cg_fwd(const VecCall& c, cudaStream_t s);
+int launch_cg_bwd(const VecCall& c, cudaStream_t s);
+int launch_cg_strided(const VecCall& c, int mode, cudaStream_t s);  // mode 0 fwd, 1 back0, 2 back1
+int launch_diag_fwd(const VecCall& c, cudaStream_t s);
+int launch_diag_bwd(const VecCall& c, cudaStream_t s);
+int launch_spharm(const std::vector<PartView>& r, const PartView& x, const CellGrid& cg, int flags, cudaStream_t s);
+
+long long launch_count();
+const std::string& last_error();
+
+}  // namespace gelib_b200

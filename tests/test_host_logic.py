@@ -1,0 +1,158 @@
+"""CPU-side checks of the shipped library: symbol table of the C ABI, host helpers (coefficients, type
+calculus, triple schedule), descriptor canonicalisation and argument validation.  No kernel is launched."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol(cabi):
+    from gelib_b200 import _lib
+    header = open(os.path.join(ROOT, "include", "gelib_b200.h")).read()
+    declared = set(re.findall(r"\b(gelib_[A-Za-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    for name in declared:
+        assert hasattr(cabi, name), name
+    assert declared == set(_lib.SYMBOLS), declared ^ set(_lib.SYMBOLS)
+    assert b"sm_100a" in cabi.gelib_version()
+
+
+def test_coefficients_match_oracle(cabi, oracle):
+    for (l1, l2, l) in [(1, 2, 2), (2, 2, 2), (3, 4, 5), (6, 6, 6), (8, 8, 8), (6, 6, 0), (0, 5, 5), (12, 12, 10)]:
+        C = np.zeros((2 * l1 + 1, 2 * l2 + 1), np.float32)
+        assert cabi.gelib_CGmatrix(l1, l2, l, C.ctypes.data) == 0
+        assert np.abs(C - oracle.cg_matrix(l1, l2, l)).max() <= 1.2e-7
+        for m1 in (-l1, 0, l1):
+            for m2 in (-l2, 0, l2):
+                if abs(m1 + m2) <= l:
+                    assert abs(cabi.gelib_CGcoefficient(l1, l2, l, m1, m2) - oracle.cg_coeff(l1, l2, l, m1, m2)) < 1e-12
+    assert cabi.gelib_CGmatrix(1, 1, 3, C.ctypes.data) == 1  # triangle violated -> skipped
+
+
+def test_type_product_and_schedule_match_oracle(oracle):
+    from gelib_b200 import backend as gb
+    from gelib_b200._lib import lib
+    for tau_x, tau_y, maxl in [({0: 2, 1: 3, 2: 1}, {0: 1, 1: 2}, -1), ({l: 4 for l in range(5)}, {l: 4 for l in range(5)}, 4),
+                               ({1: 2, 3: 1}, {2: 5}, 3)]:
+        for diag in (False, True):
+            if diag and set(tau_x.values()) | set(tau_y.values()) != {next(iter(tau_x.values()))}:
+                continue
+            tx, ty = gb.SO3type(tau_x), gb.SO3type(tau_y)
+            got = (tx.DiagCGproduct(ty, maxl) if diag else tx.CGproduct(ty, maxl)).get_parts()
+            want = oracle.cg_type(tau_x, tau_y, maxl, diag)
+            assert got == want
+            rl = sorted(want)
+            cap = 4096
+            out = (ctypes.c_int * (4 * cap))()
+            arr = lambda v: (ctypes.c_int * len(v))(*v)
+            k = lib().gelib_SO3vec_CGproduct_schedule(len(tau_x), arr(list(tau_x)), arr(list(tau_x.values())), len(tau_y),
+                                                      arr(list(tau_y)), arr(list(tau_y.values())), len(rl), arr(rl),
+                                                      1 if diag else 0, cap, out)
+            got_tr = [tuple(out[4 * i:4 * i + 4]) for i in range(k)]
+            assert got_tr == oracle.triples(tau_x, tau_y, set(rl), diag)
+
+
+def test_maxl6_schedule_has_175_triples():
+    from gelib_b200._lib import lib
+    ls = list(range(7))
+    ns = [32] * 7
+    arr = lambda v: (ctypes.c_int * len(v))(*v)
+    out = (ctypes.c_int * (4 * 400))()
+    assert lib().gelib_SO3vec_CGproduct_schedule(7, arr(ls), arr(ns), 7, arr(ls), arr(ns), 7, arr(ls), 0, 400, out) == 175
+
+
+def _fake(shape, strides, ptr=0x10000):
+    from gelib_b200._lib import Tensor5
+    t = Tensor5()
+    t.base = ptr
+    for i in range(5):
+        t.dims[i] = shape[i]
+        t.strides[i] = strides[i]
+    return t
+
+
+def test_validation_happens_before_any_cuda_call(cabi):
+    """Arguments the reference would GELIB_SKIP come back as GELIB_SKIPPED with its message
+    (cuda/SO3part_addCGproduct.cu:189-214, core/CGproduct.hpp:48-49); nothing is launched."""
+    from gelib_b200._lib import GELIB_INVALID, GELIB_SKIPPED
+    dense = lambda b, L, n: _fake((b, 1, 1, L, n), (L * n * 2, 0, 0, n * 2, 2))
+    by = ctypes.byref
+    r, x, y = dense(4, 5, 4), dense(4, 5, 2), dense(3, 5, 2)
+    assert cabi.gelib_SO3part_addCGproduct(by(r), by(x), by(y), 0, 0, None) == GELIB_SKIPPED
+    assert b"batch dimensions cannot be reconciled" in cabi.gelib_last_error()
+    r, x, y = dense(4, 7, 4), dense(4, 3, 2), dense(4, 3, 2)   # l=3 from 1 x 1
+    assert cabi.gelib_SO3part_addCGproduct(by(r), by(x), by(y), 0, 0, None) == GELIB_SKIPPED
+    assert b"|l1-l_2| <= l <= l1+l2 not satisfied" in cabi.gelib_last_error()
+    r, x, y = dense(4, 3, 4), dense(4, 3, 2), dense(4, 3, 2)
+    assert cabi.gelib_SO3part_addCGproduct(by(r), by(x), by(y), 1, 0, None) == GELIB_SKIPPED
+    assert b"fragment dimension of r not large enough" in cabi.gelib_last_error()
+    r, x, y = dense(4, 3, 4), dense(4, 3, 2), dense(4, 3, 3)
+    assert cabi.gelib_SO3part_addDiagCGproduct(by(r), by(x), by(y), 0, 0, None) == GELIB_INVALID
+    assert b"N1==N2" in cabi.gelib_last_error()
+    assert cabi.gelib_SO3part_addCGproduct(None, by(x), by(y), 0, 0, None) == GELIB_INVALID
+    g = _fake((4, 2, 3, 3, 4), (72 * 2, 36 * 2, 12 * 2, 8, 2))
+    xg = _fake((4, 2, 2, 3, 2), (48, 24, 12, 4, 2))
+    assert cabi.gelib_SO3part_addCGproduct_back0(by(xg), by(g), by(dense(4, 3, 2)), 0, 0, None) == GELIB_SKIPPED
+    assert b"grid dimensions cannot be reconciled" in cabi.gelib_last_error()
+    assert cabi.gelib_status_string(GELIB_SKIPPED).startswith(b"skipped")
+
+
+def test_cpu_tensors_are_refused_not_computed():
+    """There is no CPU path in the product: a CPU tensor raises instead of silently falling back."""
+    import gelib_b200 as G
+    x, y = G.SO3part.randn(2, 1, 2), G.SO3part.randn(2, 1, 2)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        G.CGproduct(x, y, 1)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        G.SO3part.spharm(2, torch.randn(2, 3, 4))
+
+
+def test_descriptor_canonical_form():
+    """core/Gpart.hpp:450-469: 3-D -> (b,1,1,L,n), 4-D -> (b,g,1,L,n), >5-D grids fused; float strides."""
+    from gelib_b200 import _lib
+
+    class FakeCuda(torch.Tensor):
+        is_cuda = True
+
+    def desc(t, **kw):
+        return _lib.descriptor(t.as_subclass(FakeCuda), **kw)
+
+    d = desc(torch.zeros(4, 5, 6, dtype=torch.complex64))
+    assert list(d.dims) == [4, 1, 1, 5, 6] and list(d.strides) == [60, 0, 0, 12, 2]
+    d = desc(torch.zeros(4, 3, 5, 6, dtype=torch.complex64))
+    assert list(d.dims) == [4, 3, 1, 5, 6] and list(d.strides) == [180, 60, 0, 12, 2]
+    d = desc(torch.zeros(4, 2, 3, 5, 6, dtype=torch.complex64))
+    assert list(d.dims) == [4, 2, 3, 5, 6] and list(d.strides) == [360, 180, 60, 12, 2]
+    d = desc(torch.zeros(4, 2, 3, 2, 5, 6, dtype=torch.complex64))
+    assert list(d.dims) == [4, 12, 1, 5, 6] and list(d.strides) == [720, 60, 0, 12, 2]
+    d = desc(torch.zeros(1, 5, 6, dtype=torch.complex64).expand(4, 5, 6))
+    assert list(d.strides)[0] == 0
+    d = desc(torch.zeros(4, 3, 6), real=True)
+    assert list(d.dims) == [4, 1, 1, 3, 6] and list(d.strides) == [18, 0, 0, 6, 1]
+    with pytest.raises(RuntimeError):
+        desc(torch.zeros(4, 2, 3, 2, 5, 6, dtype=torch.complex64).transpose(1, 2))
+    with pytest.raises(RuntimeError):
+        desc(torch.zeros(4, 5, 6))
+
+
+def test_python_surface_matches_reference_names():
+    import gelib_b200 as G
+    for name in ["SO3part", "SO3vec", "SO3partArr", "SO3vecArr", "SO3type", "SO3weights", "SO3linear", "SO3element",
+                 "SO3irrep", "CGproduct", "DiagCGproduct", "SO3part_CGproductFn", "SO3part_DiagCGproductFn",
+                 "SO3vec_CGproductFn", "SO3vec_DiagCGproductFn", "common_batch"]:
+        assert hasattr(G, name), name
+    for name in ["add_CGproduct", "add_CGproduct_back0", "add_CGproduct_back1", "add_DiagCGproduct",
+                 "add_DiagCGproduct_back0", "add_DiagCGproduct_back1", "add_spharm", "view"]:
+        assert hasattr(G.backend.SO3part, name), name
+    for name in ["addCGproduct", "addCGproduct_back0", "addCGproduct_back1", "addDiagCGproduct",
+                 "addDiagCGproduct_back0", "addDiagCGproduct_back1", "get_tau", "view"]:
+        assert hasattr(G.backend.SO3vec, name), name
+    R = G.SO3element.random()
+    assert torch.allclose(R @ R.t(), torch.eye(3), atol=1e-5) and abs(float(torch.det(R)) - 1) < 1e-5
+    D = G.SO3irrep(3).matrix(R)
+    assert torch.allclose(D @ D.conj().t(), torch.eye(7, dtype=torch.complex64), atol=1e-5)
