@@ -28,11 +28,13 @@ int parse_parts(const char* fn, const char* name, int n, const gelib_tensor5* t,
   if (n > kMaxParts) return fail(GELIB_SKIPPED, fn, std::string(name) + " has more than GELIB_MAX_PARTS parts");
   std::vector<std::pair<int, int>> order;
   for (int i = 0; i < n; i++) {
-    if (!t[i].base) return fail(GELIB_INVALID, fn, std::string("null data pointer in ") + name);
+    bool empty = false;
     for (int d = 0; d < 5; d++) {
       if (t[i].dims[d] < 0) return fail(GELIB_INVALID, fn, std::string("negative dimension in ") + name);
       if (t[i].strides[d] < 0) return fail(GELIB_INVALID, fn, std::string("negative stride in ") + name);
+      if (t[i].dims[d] == 0) empty = true;
     }
+    if (!t[i].base && !empty) return fail(GELIB_INVALID, fn, std::string("null data pointer in ") + name);
     if (!real3 && t[i].dims[3] % 2 == 0)
       return fail(GELIB_SKIPPED, fn, std::string("dims[3] of ") + name + " is not of the form 2l+1");
     order.push_back({real3 ? 0 : (t[i].dims[3] - 1) / 2, i});
