@@ -28,7 +28,7 @@ struct FwdArgs {
   PartView x[kMaxParts], y[kMaxParts], r[kMaxParts];
   int xoff[kMaxParts], yoff[kMaxParts];  // float offset of each part inside a cell's shared-memory block
   int xnp[kMaxParts], ynp[kMaxParts];    // padded channel counts (complex) of the staged rows
-  int nx, ny;
+  int nx, ny, nr;
   int cell_floats;                       // shared-memory floats per cell (x block then y block)
   CellGrid cg;
   const Triple* triples;
@@ -86,9 +86,12 @@ template <int TA, int WA, int NBL, bool VEC>
 __global__ void __launch_bounds__(128) cg_fwd_kernel(const __grid_constant__ FwdArgs A) {
   constexpr int WC = 32 / (WA * NBL);
   static_assert(WC * WA * NBL == 32, "lane layout must fill a warp");
-  extern __shared__ __align__(16) float smem[];
+  extern __shared__ __align__(16) float smem_raw[];
+  long long* roff = reinterpret_cast<long long*>(smem_raw);  // [WC][kMaxParts] output offsets of the CTA's cells
+  float* smem = smem_raw + 2 * WC * kMaxParts;
 
   const long long cell0 = (long long)blockIdx.x * WC;
+  fill_cell_offsets(roff, A.r, A.nr, A.cg, cell0, WC);
   for (int c = 0; c < WC; c++) {
     const long long cell = cell0 + c;
     if (cell >= A.cg.ncells) break;
@@ -118,7 +121,7 @@ __global__ void __launch_bounds__(128) cg_fwd_kernel(const __grid_constant__ Fwd
     const float* xs = blk + A.xoff[t.xi] + 2 * i0;
     const float* ys = blk + A.yoff[t.yi];
     const float* cp = A.coeffs + t.coff;
-    float* rbase = cell_ok ? rp.base + cell_offset(rp, A.cg, cell) + 2LL * (t.offs + A.offs_extra) : nullptr;
+    float* rbase = rp.base + roff[lc * kMaxParts + t.ri] + 2LL * (t.offs + A.offs_extra);
 
     for (int m = -l; m <= l; m++) {
       const int lo = max(-l1, m - l2), hi = min(l1, m + l2);
@@ -249,8 +252,9 @@ int launch_cg_fwd(const VecCall& c, cudaStream_t s) {
   for (size_t i = 0; i < c.r.size(); i++) a.r[i] = c.r[i];
   a.nx = (int)c.x.size();
   a.ny = (int)c.y.size();
+  a.nr = (int)c.r.size();
   a.cell_floats = off;
-  const size_t smem = ((size_t)off * WC + 128) * sizeof(float);  // +128 floats: tiles may read past the last row
+  const size_t smem = ((size_t)off * WC + 128 + 2 * WC * kMaxParts) * sizeof(float);  // +128 floats: tiles may read past the last row
   if (smem > 200 * 1024) return -1;                             // caller falls back to the strided kernel
 
   // ---- jobs: enough CTAs to fill the machine several times over

@@ -32,12 +32,32 @@ struct CellGrid {
 };
 
 __host__ __device__ inline long long cell_offset(const PartView& p, const CellGrid& cg, long long cell) {
+  if (cg.G0 == 1 && cg.G1 == 1) return cell * p.sb;  // plain SO3parts: no grid
+  if (cg.ncells < 0x7fffffffLL) {                     // 32-bit division is several times cheaper
+    const unsigned c = (unsigned)cell;
+    const unsigned g1 = c % (unsigned)cg.G1, t = c / (unsigned)cg.G1;
+    const unsigned g0 = t % (unsigned)cg.G0, b = t / (unsigned)cg.G0;
+    return (long long)b * p.sb + (long long)g0 * p.sg0 + (long long)g1 * p.sg1;
+  }
   const int g1 = (int)(cell % cg.G1);
   const long long t = cell / cg.G1;
   const int g0 = (int)(t % cg.G0);
   const long long b = t / cg.G0;
   return b * p.sb + (long long)g0 * p.sg0 + (long long)g1 * p.sg1;
 }
+
+#ifdef __CUDACC__
+// Float offsets of the CTA's cells into every part of one vector, computed once so that no inner loop
+// divides: dst[c * kMaxParts + part] for the cells cell0 .. cell0 + WC - 1.
+__device__ __forceinline__ void fill_cell_offsets(long long* dst, const PartView* parts, int nparts,
+                                                  const CellGrid& cg, long long cell0, int WC) {
+  for (int e = threadIdx.x; e < WC * nparts; e += blockDim.x) {
+    const int c = e / nparts, p = e - c * nparts;
+    const long long cell = cell0 + c;
+    dst[c * kMaxParts + p] = cell < cg.ncells ? cell_offset(parts[p], cg, cell) : 0;
+  }
+}
+#endif
 
 // One (l1,l2)->l term of a product.  xi/yi/ri index the part arrays of the call, offs is the first
 // output channel of the term inside part ri, coff the offset of its band coefficients in the plan's
