@@ -282,6 +282,8 @@ __global__ void __launch_bounds__(256) diag_bwd_kernel(const __grid_constant__ D
   }
 }
 
+}  // namespace
+
 // Items of a diagonal product: for every (xi, yi) pair (a maximal run of the schedule) and every row
 // index m reachable by some l, the dense coefficient table [m1 in band][l among the valid ones].
 void build_diag_items(DevicePlan& p, const std::vector<PartSig>& xs, const std::vector<PartSig>& ys,
@@ -321,6 +323,8 @@ void build_diag_items(DevicePlan& p, const std::vector<PartSig>& xs, const std::
     ti = tj;
   }
 }
+
+namespace {
 
 struct DiagSetup {
   DiagArgs a;
@@ -400,6 +404,10 @@ int setup(const VecCall& c, DiagArgs& a, DevicePlan** plan_out, int* max_nl_out)
 
 int launch_diag_fwd(const VecCall& c, cudaStream_t s) {
   static const char* fn = "SO3vec_addDiagCGproduct";
+  {
+    const int st = launch_diag_fwd_fast(c, s);  // one cell per CTA, 32 or 64 channels per warp row
+    if (st != -1) return st;
+  }
   DiagArgs a;
   DevicePlan* plan = nullptr;
   int max_nl = 0;

@@ -33,6 +33,10 @@ int launch_cg_bwd(const VecCall& c, cudaStream_t s);
 int launch_cg_strided(const VecCall& c, int mode, cudaStream_t s);  // mode 0 fwd, 1 back0, 2 back1
 int launch_diag_fwd(const VecCall& c, cudaStream_t s);
 int launch_diag_bwd(const VecCall& c, cudaStream_t s);
+int launch_diag_fwd_fast(const VecCall& c, cudaStream_t s);  // -1 when the call does not qualify
+// Work items of a diagonal product (defined in diag.cu): {first triple | nl<<16, m, coefficient offset, padded nl}
+void build_diag_items(DevicePlan& p, const std::vector<PartSig>& xs, const std::vector<PartSig>& ys,
+                      const std::vector<PartSig>& rs, int* max_nl);
 int launch_spharm(const std::vector<PartView>& r, const PartView& x, const CellGrid& cg, int flags, cudaStream_t s);
 
 long long launch_count();
