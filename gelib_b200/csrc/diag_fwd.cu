@@ -33,8 +33,9 @@ struct DiagFwdArgs {
   CellGrid cg;
   const float* coeffs;
   const int4* recs;
-  const int* chunks;    // 8 ints per chunk: item_begin, item_end, coef_begin, coef_floats, rec_begin, rec_count, -, -
-  const int* item_rec;  // record offset of every item inside its chunk
+  // 8 ints per chunk: number of items, -, coef_begin, coef_floats, rec_begin, rec_count, -, -.  The record block of a
+  // chunk starts with one int per item (padded to int4s): the int4 index of the item's record inside the block.
+  const int* chunks;
   int nchunks, chunks_per_z;
   int offs_extra;
   int accumulate;
@@ -192,10 +193,10 @@ __global__ void __launch_bounds__(256) diag_fwd_cell_kernel(const __grid_constan
     }
     __syncthreads();
     const int* ck = A.chunks + 8 * c;
-    const int ib = __ldg(ck), ie = __ldg(ck + 1);
+    const int nit = __ldg(ck);
     const int CB = BUF + buf * kBufFloats, RB = CB + kCoefCap;
-    for (int it = ib + warp; it < ie; it += nwarps) {
-      const int rec = RB + 4 * __ldg(&A.item_rec[it]);
+    for (int it = warp; it < nit; it += nwarps) {
+      const int rec = RB + 4 * __float_as_int(smem[RB + it]);
       const int4 h = *reinterpret_cast<const int4*>(&smem[rec]);
       const int nl = h.x & 255, band = (h.x >> 8) & 255, nlp = h.x >> 16;
       const int xi = XS + 2 * W * (h.y & 0xffff) + lane_off, yi = YS + 2 * W * (h.y >> 16) + lane_off;
@@ -239,27 +240,43 @@ void build_plan(DevicePlan& p, const std::vector<PartSig>& xs, const std::vector
   p.h_items.clear();
   p.h_jobs.clear();
   p.sched.coeffs.clear();
-  std::vector<int> chunks, item_rec;
+  std::vector<int> chunks;
   size_t i = 0;
   while (i < all.size()) {
-    const int item_begin = (int)i, coef_begin = (int)p.sched.coeffs.size(), rec_begin = (int)p.h_items.size();
+    // greedy fill within the caps; then keep a multiple of 8 items (one round per warp) when possible
+    size_t j = i;
     int nc = 0, nr = 0;
-    while (i < all.size() && (nc == 0 || (nc + (int)all[i].coef.size() <= kCoefCap && nr + (int)all[i].v.size() <= kRecCap))) {
-      all[i].v[0].z = nc;  // coefficient index inside the chunk
-      item_rec.push_back(nr);
-      for (const int4& q : all[i].v) p.h_items.push_back(q);
-      p.sched.coeffs.insert(p.sched.coeffs.end(), all[i].coef.begin(), all[i].coef.end());
-      nc += (int)all[i].coef.size();
-      nr += (int)all[i].v.size();
-      i++;
+    while (j < all.size()) {
+      const int tab = (int)(j + 1 - i + 3) / 4;  // int4s of the item-offset table if item j is taken
+      if (j > i && (nc + (int)all[j].coef.size() > kCoefCap || tab + nr + (int)all[j].v.size() > kRecCap)) break;
+      nc += (int)all[j].coef.size();
+      nr += (int)all[j].v.size();
+      j++;
     }
-    const int v[8] = {item_begin, (int)i, coef_begin, nc, rec_begin, nr, 0, 0};
+    if (j - i > 8 && j < all.size()) j = i + (j - i) / 8 * 8;
+    const int nit = (int)(j - i), tab = (nit + 3) / 4;
+    const int coef_begin = (int)p.sched.coeffs.size(), rec_begin = (int)p.h_items.size();
+    std::vector<int> offs(4 * tab, 0);
+    nc = 0;
+    nr = tab;
+    for (size_t q = i; q < j; q++) {
+      offs[q - i] = nr;
+      all[q].v[0].z = nc;  // coefficient index inside the chunk
+      nc += (int)all[q].coef.size();
+      nr += (int)all[q].v.size();
+    }
+    for (int t = 0; t < tab; t++) p.h_items.push_back(make_int4(offs[4 * t], offs[4 * t + 1], offs[4 * t + 2], offs[4 * t + 3]));
+    for (size_t q = i; q < j; q++) {
+      for (const int4& v : all[q].v) p.h_items.push_back(v);
+      p.sched.coeffs.insert(p.sched.coeffs.end(), all[q].coef.begin(), all[q].coef.end());
+    }
+    const int v[8] = {nit, 0, coef_begin, nc, rec_begin, nr, 0, 0};
     chunks.insert(chunks.end(), v, v + 8);
+    i = j;
   }
-  // jobs = [number of chunks, chunk table, record offset of every item]
+  // jobs = [number of chunks, chunk table]
   p.h_jobs.push_back((int)chunks.size() / 8);
   p.h_jobs.insert(p.h_jobs.end(), chunks.begin(), chunks.end());
-  p.h_jobs.insert(p.h_jobs.end(), item_rec.begin(), item_rec.end());
 }
 
 }  // namespace
@@ -315,7 +332,6 @@ int launch_diag_fwd_fast(const VecCall& c, cudaStream_t s) {
   a.coeffs = plan->coeffs;
   a.recs = plan->items;
   a.chunks = plan->jobs + 1;
-  a.item_rec = plan->jobs + 1 + 8 * nchunks;
   a.nchunks = nchunks;
   a.offs_extra = c.offs_extra;
   a.accumulate = (c.flags & GELIB_OVERWRITE) ? 0 : 1;
