@@ -442,6 +442,10 @@ int launch_diag_fwd(const VecCall& c, cudaStream_t s) {
 
 int launch_diag_bwd(const VecCall& c, cudaStream_t s) {
   static const char* fn = "SO3vec_addDiagCGproduct_back";
+  {
+    const int st = launch_diag_bwd_fast(c, s);  // one cell per CTA, 32 channels per warp row
+    if (st != -1) return st;
+  }
   DiagArgs a;
   DevicePlan* plan = nullptr;
   int max_nl = 0;

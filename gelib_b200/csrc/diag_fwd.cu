@@ -281,6 +281,16 @@ void build_plan(DevicePlan& p, const std::vector<PartSig>& xs, const std::vector
 
 }  // namespace
 
+// The plan of the one-cell-per-CTA diagonal kernels (forward and backward share it).
+DevicePlan* diag_cell_plan(const VecCall& c, const std::vector<int>& xrow0, const std::vector<int>& yrow0) {
+  std::vector<int> key = {5 /*family*/, (int)c.x.size(), (int)c.y.size(), (int)c.r.size(), c.x[0].n};
+  for (const auto& p : c.x) key.push_back(p.l);
+  for (const auto& p : c.y) key.push_back(p.l);
+  for (const auto& p : c.r) { key.push_back(p.l); key.push_back(p.n); }
+  const auto xs = sig_of(c.x), ys = sig_of(c.y), rs = sig_of(c.r);
+  return get_plan(key, [&](DevicePlan& p) { build_plan(p, xs, ys, rs, xrow0, yrow0); });
+}
+
 int launch_diag_fwd_fast(const VecCall& c, cudaStream_t s) {
   static const char* fn = "SO3vec_addDiagCGproduct";
   if (c.x.empty() || c.y.empty() || c.r.empty()) return -1;
@@ -319,12 +329,7 @@ int launch_diag_fwd_fast(const VecCall& c, cudaStream_t s) {
   const int W = two ? 64 : 32;
   const size_t smem = ((size_t)2 * (a.xrows + a.yrows) * W + 2 * kMaxParts + 2 * kBufFloats) * sizeof(float);
   if (smem > 200 * 1024) return -1;
-  std::vector<int> key = {5 /*family*/, (int)c.x.size(), (int)c.y.size(), (int)c.r.size(), n};
-  for (const auto& p : c.x) key.push_back(p.l);
-  for (const auto& p : c.y) key.push_back(p.l);
-  for (const auto& p : c.r) { key.push_back(p.l); key.push_back(p.n); }
-  const auto xs = sig_of(c.x), ys = sig_of(c.y), rs = sig_of(c.r);
-  DevicePlan* plan = get_plan(key, [&](DevicePlan& p) { build_plan(p, xs, ys, rs, xrow0, yrow0); });
+  DevicePlan* plan = diag_cell_plan(c, xrow0, yrow0);
   if (!plan) return GELIB_CUDA_ERROR;
   const int nchunks = plan->h_jobs.empty() ? 0 : plan->h_jobs[0];
   if (nchunks == 0 || c.cg.ncells == 0) return GELIB_OK;

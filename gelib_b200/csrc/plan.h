@@ -34,6 +34,7 @@ int launch_cg_strided(const VecCall& c, int mode, cudaStream_t s);  // mode 0 fw
 int launch_diag_fwd(const VecCall& c, cudaStream_t s);
 int launch_diag_bwd(const VecCall& c, cudaStream_t s);
 int launch_diag_fwd_fast(const VecCall& c, cudaStream_t s);  // -1 when the call does not qualify
+int launch_diag_bwd_fast(const VecCall& c, cudaStream_t s);  // -1 when the call does not qualify
 // Work items of a diagonal product (defined in diag.cu): {first triple | nl<<16, m, coefficient offset, padded nl}
 void build_diag_items(DevicePlan& p, const std::vector<PartSig>& xs, const std::vector<PartSig>& ys,
                       const std::vector<PartSig>& rs, int* max_nl);
