@@ -191,12 +191,26 @@ int run_product(const char* fn, bool diag, int mode, int nr, const gelib_tensor5
   cudaStream_t s = (cudaStream_t)stream;
   if (mode == 0) {
     st = -1;
-    if (c.dense_channels && !c.r_bcast) st = diag ? launch_diag_fwd(c, s) : launch_cg_fwd(c, s);
+    if (c.dense_channels && !c.r_bcast) {
+      if (diag) {
+        st = launch_diag_fwd(c, s);
+      } else {
+        st = launch_cg_narrow_fwd(c, s);
+        if (st == -1) st = launch_cg_fwd(c, s);
+      }
+    }
     if (st == -1) st = launch_cg_strided(c, 0, s);
     return st;
   }
   st = -1;
-  if (c.dense_channels) st = diag ? launch_diag_bwd(c, s) : launch_cg_bwd(c, s);
+  if (c.dense_channels) {
+    if (diag) {
+      st = launch_diag_bwd(c, s);
+    } else {
+      st = launch_cg_narrow_bwd(c, s);
+      if (st == -1) st = launch_cg_bwd(c, s);
+    }
+  }
   if (st == -1) {
     st = GELIB_OK;
     if (!c.xg.empty()) st = launch_cg_strided(c, 1, s);
