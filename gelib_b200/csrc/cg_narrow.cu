@@ -202,7 +202,8 @@ __device__ __forceinline__ void bwd_l2(const NarrowArgs& A, const float* xs_cell
 #pragma unroll
   for (int s = 0; s < ilog2n(NS); s++) p |= ((lic >> s) & 1) << (ilog2n(NS) - 1 - s);
   const bool writer = (lic >> ilog2n(NS)) == 0;  // lanes beyond NS hold copies after the all-reduce steps
-  float2 yreg[NS], ygacc[NS];
+  constexpr int LYP = LY + 1;
+  float2 yreg[NS], ygacc[LYP];  // y column in permuted slot order (for the butterfly); yg column in natural order
   const PartView& yp = A.y[yi];
   {
     const float* yb = yp.base + (ok ? cell_offset(yp, A.cg, cell) : 0) + 2 * n2l;
@@ -210,8 +211,9 @@ __device__ __forceinline__ void bwd_l2(const NarrowArgs& A, const float* xs_cell
     for (int sl = 0; sl < NS; sl++) {
       const int j = sl ^ p;
       yreg[sl] = (ok && j < LY) ? __ldg(reinterpret_cast<const float2*>(yb + (long long)j * yp.sm)) : make_float2(0.f, 0.f);
-      ygacc[sl] = make_float2(0.f, 0.f);
     }
+#pragma unroll
+    for (int j = 0; j < LYP; j++) ygacc[j] = make_float2(0.f, 0.f);
   }
   const int jown = p;  // after the butterfly slot 0 of this lane is the sum for m2 index p
   for (int xi = 0; xi < A.nx; xi++) {
@@ -226,33 +228,22 @@ __device__ __forceinline__ void bwd_l2(const NarrowArgs& A, const float* xs_cell
       const float* Cm = A.coeffs + tr.coff;
       for (int n1i = 0; n1i < n1; n1i++) {
         __syncwarp();
-        if (A.do_y) {
-          // A[m][j] with rows of NS entries (zero beyond LY), as in the forward pass
-          const int total = (2 * l + 1) * NS;
-          for (int e = lic; e < total; e += CW) {
-            const int mi = e / NS, j = e - mi * NS;
-            const int m1 = (mi - l) - (j - l2);
-            float2 v = make_float2(0.f, 0.f);
-            if (j < LY && m1 >= -l1 && m1 <= l1) {
-              const float c = __ldg(Cm + (m1 + l1) * LY + j);
-              const float2 xv = *reinterpret_cast<const float2*>(xs + 2 * ((m1 + l1) * A.n1max + n1i));
-              v = make_float2(c * xv.x, c * xv.y);
-            }
-            *reinterpret_cast<float2*>(cx + 2 * e) = v;
-          }
-        }
+        if (A.do_y) build_A<LY>(cx, xs, Cm, l, l1, l2, A.n1max, n1i, lic, CW);
         __syncwarp();
         const float* gb = gp.base + goff[tr.ri] + 2LL * (tr.offs + A.offs_extra + n1i * A.n2 + n2l);
+        float2 gnext = ok ? __ldcs(reinterpret_cast<const float2*>(gb)) : make_float2(0.f, 0.f);
         for (int mi = 0; mi <= 2 * l; mi++) {
-          const float2 g = ok ? __ldcs(reinterpret_cast<const float2*>(gb + (long long)mi * gp.sm)) : make_float2(0.f, 0.f);
+          const float2 g = gnext;
+          if (mi < 2 * l && ok) gnext = __ldcs(reinterpret_cast<const float2*>(gb + (long long)(mi + 1) * gp.sm));
           if (A.do_y) {
-            const float* row = cx + 2 * mi * NS;
+            const float* row = cx + 2 * mi * LYP;
 #pragma unroll
-            for (int sl = 0; sl < NS; sl++) {
-              const float2 a = *reinterpret_cast<const float2*>(row + 2 * (sl ^ p));
-              // g conj(A)
-              ygacc[sl].x = fmaf(g.x, a.x, ygacc[sl].x); ygacc[sl].x = fmaf(g.y, a.y, ygacc[sl].x);
-              ygacc[sl].y = fmaf(g.y, a.x, ygacc[sl].y); ygacc[sl].y = fmaf(-g.x, a.y, ygacc[sl].y);
+            for (int j = 0; j < LYP; j += 2) {  // g conj(A), two entries per broadcast load
+              const float4 a = *reinterpret_cast<const float4*>(row + 2 * j);
+              ygacc[j].x = fmaf(g.x, a.x, ygacc[j].x); ygacc[j].x = fmaf(g.y, a.y, ygacc[j].x);
+              ygacc[j].y = fmaf(g.y, a.x, ygacc[j].y); ygacc[j].y = fmaf(-g.x, a.y, ygacc[j].y);
+              ygacc[j + 1].x = fmaf(g.x, a.z, ygacc[j + 1].x); ygacc[j + 1].x = fmaf(g.y, a.w, ygacc[j + 1].x);
+              ygacc[j + 1].y = fmaf(g.y, a.z, ygacc[j + 1].y); ygacc[j + 1].y = fmaf(-g.x, a.w, ygacc[j + 1].y);
             }
           }
           if (A.do_x) {
@@ -281,19 +272,16 @@ __device__ __forceinline__ void bwd_l2(const NarrowArgs& A, const float* xs_cell
     const PartView& ygp = A.yg[yi];
     float* yb = ygp.base + cell_offset(ygp, A.cg, cell) + 2 * n2l;
 #pragma unroll
-    for (int sl = 0; sl < NS; sl++) {
-      const int j = sl ^ p;
-      if (j < LY) {
-        float* q = yb + (long long)j * ygp.sm;
-        if (A.y_atomic) {
-          atomicAdd(q, ygacc[sl].x);
-          atomicAdd(q + 1, ygacc[sl].y);
-        } else {
-          float2 o = *reinterpret_cast<float2*>(q);
-          o.x += ygacc[sl].x;
-          o.y += ygacc[sl].y;
-          *reinterpret_cast<float2*>(q) = o;
-        }
+    for (int j = 0; j < LY; j++) {
+      float* q = yb + (long long)j * ygp.sm;
+      if (A.y_atomic) {
+        atomicAdd(q, ygacc[j].x);
+        atomicAdd(q + 1, ygacc[j].y);
+      } else {
+        float2 o = *reinterpret_cast<float2*>(q);
+        o.x += ygacc[j].x;
+        o.y += ygacc[j].y;
+        *reinterpret_cast<float2*>(q) = o;
       }
     }
   }
