@@ -71,6 +71,12 @@ def algorithmic_work(tx, ty, maxl, B, diag):
     return {"macs": macs * B, "fwd_bytes": 8 * B * (xin + rout), "bwd_bytes": 8 * B * (rout + 2 * xin), "tau_r": out}
 
 
+# DRAM traffic of one launch relative to its algorithmic bytes, from the ncu captures summarised in
+# profiles/cg_fwd_kernel_cfg3_b296.md and profiles/cg_bwd_kernel_cfg3_b296.md (dram__bytes_read + dram__bytes_write of
+# a batch-296 launch; traffic grows in proportion to the batch, so the ratio carries over to the full batch).
+TRAFFIC_RATIO = {("cfg3", "forward"): 0.98, ("cfg3", "backward"): 1.002}
+
+
 def measured_peak():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -92,7 +98,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                          "--format=csv,noheader,nounits", "-lms", "20"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -132,6 +138,15 @@ class ClockSampler:
 # ---- CPU legs -------------------------------------------------------------------------------------------------
 
 
+def host_threads():
+    """Host threads the CPU legs use: every core this process may run on (torchrun sets OMP_NUM_THREADS=1, which
+    would otherwise silently make the OpenMP oracle single-threaded)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_fwd_bwd(O, tx, ty, maxl, Bs, diag, nthreads, reps=1):
     """One forward + back0 + back1 of the oracle on a batch slice; returns seconds per repetition."""
     import numpy as np
@@ -158,14 +173,14 @@ def cpu_fwd_bwd(O, tx, ty, maxl, Bs, diag, nthreads, reps=1):
 def cpu_baseline(tx, ty, maxl, B, diag, budget_s=15.0):
     from oracle import oracle as O
     O.build()
-    nt = O.max_threads()
+    nt = host_threads()
     Bs = max(nt, 8)
-    t = cpu_fwd_bwd(O, tx, ty, maxl, Bs, diag, 0)
+    t = cpu_fwd_bwd(O, tx, ty, maxl, Bs, diag, nt)
     # grow the slice towards the time budget (cost is linear in the batch)
     scale = int(min(B // Bs, max(1, budget_s / 3 / max(t, 1e-4))))
     if scale > 1:
         Bs *= scale
-        t = cpu_fwd_bwd(O, tx, ty, maxl, Bs, diag, 0)
+        t = cpu_fwd_bwd(O, tx, ty, maxl, Bs, diag, nt)
     ms_full = t * 1e3 * B / Bs
     return {"value": ms_full, "unit": "ms", "cores": nt, "kind": "port",
             "sample": "oracle (CPU restatement of the reference loops, OpenMP over the batch) on %d of %d batch rows: "
@@ -181,11 +196,11 @@ def run_reference(args, tx, ty, maxl, B, diag, desc):
         return
     from oracle import oracle as O
     O.build()
-    nt = O.max_threads()
-    Bs = max(nt, 8) * 2
+    nt = host_threads()
+    Bs = max(nt, 8) * 4
     times = []
     for i in range(args.warmup + args.steps):
-        t = cpu_fwd_bwd(O, tx, ty, maxl, Bs, diag, 0)
+        t = cpu_fwd_bwd(O, tx, ty, maxl, Bs, diag, nt)
         if i >= args.warmup:
             times.append(t)
     ms = statistics.mean(times) * 1e3 * B / Bs
@@ -194,7 +209,9 @@ def run_reference(args, tx, ty, maxl, B, diag, desc):
     print(json.dumps({"impl": "reference", "metric": "cg_product_fwd_bwd_ms_per_call", "value": ms, "unit": "ms",
                       "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
                       "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-                      "data": "synthetic", "config": {"workload": desc}, "cpu_baseline": cb,
+                      "data": "synthetic",
+                      "config": {"workload": "%s: %s; per-GPU batch %d, global batch %d" % (args.workload, desc, B, B * args.gpus)},
+                      "cpu_baseline": cb,
                       "e2e": {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
@@ -204,7 +221,7 @@ def run_reference(args, tx, ty, maxl, B, diag, desc):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (for profiling small cases)")
@@ -348,7 +365,8 @@ def main():
             "cells_per_s": B * world / (tot_ms * 1e-3),
             "roofline": {"bound": "hbm", "kernel": "cg_%s_kernel" % ("fwd" if dom == "forward" else "bwd"),
                          "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": peak_kind,
-                         "traffic": None,
+                         "traffic": (TRAFFIC_RATIO[(args.workload, dom)] * (work["fwd_bytes"] if dom == "forward" else work["bwd_bytes"])
+                                     if (args.workload, dom) in TRAFFIC_RATIO else None),
                          "algorithmic_bytes_per_launch": work["fwd_bytes"] if dom == "forward" else work["bwd_bytes"],
                          "fwd": {"ms": fwd_ms, "GBps": fwd_gbs, "frac": fwd_gbs / peak},
                          "bwd": {"ms": bwd_ms, "GBps": bwd_gbs, "frac": bwd_gbs / peak},

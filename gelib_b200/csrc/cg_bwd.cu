@@ -23,6 +23,7 @@
 // gradient is the sum over cells).  The order in which warps add into a row is not fixed, so gradients are
 // reproducible to rounding (about 1e-7 relative), not bitwise.  All shared-memory addressing is 32-bit.
 #include <algorithm>
+#include <cstdlib>
 
 #include "plan.h"
 
@@ -390,7 +391,7 @@ int launch_cg_bwd(const VecCall& c, cudaStream_t s) {
   for (size_t i = 0; i < c.y.size(); i++) if (a.ynp[i] > 65535) return -1;
   const size_t smem = ((size_t)6 * WC * kMaxParts + (size_t)2 * WC * off) * sizeof(float);
   if (smem > 220 * 1024) return -1;  // caller falls back to the strided kernels
-  const int nwarps = 8;
+  const int nwarps = getenv("GELIB_BWD_WARPS") ? atoi(getenv("GELIB_BWD_WARPS")) : 8;
 
   std::vector<int> key = {3 /*family*/, best, vec ? 1 : 0, (int)c.x.size(), (int)c.y.size(), (int)c.r.size()};
   for (const auto& p : c.x) { key.push_back(p.l); key.push_back(p.n); }
