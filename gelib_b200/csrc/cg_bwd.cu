@@ -344,6 +344,13 @@ inline int align4(int v) { return (v + 3) / 4 * 4; }
 
 int launch_cg_bwd(const VecCall& c, cudaStream_t s) {
   static const char* fn = "SO3vec_addCGproduct_back";
+  // channel counts that are multiples of 32 with both gradients requested go to the tensor cores;
+  // GELIB_B200_BWD_SIMT=1 keeps them on this file's kernel (for comparisons)
+  const char* simt = getenv("GELIB_B200_BWD_SIMT");
+  if (!(simt && atoi(simt) != 0)) {
+    const int rc = launch_cg_bwd_tc(c, s);
+    if (rc != -1) return rc;
+  }
   const bool vec = c.vec_ok;
   const int UB = vec ? 2 : 1;
   int n1 = 1, n2 = 1;
@@ -391,7 +398,7 @@ int launch_cg_bwd(const VecCall& c, cudaStream_t s) {
   for (size_t i = 0; i < c.y.size(); i++) if (a.ynp[i] > 65535) return -1;
   const size_t smem = ((size_t)6 * WC * kMaxParts + (size_t)2 * WC * off) * sizeof(float);
   if (smem > 220 * 1024) return -1;  // caller falls back to the strided kernels
-  const int nwarps = getenv("GELIB_BWD_WARPS") ? atoi(getenv("GELIB_BWD_WARPS")) : 8;
+  const int nwarps = 8;
 
   std::vector<int> key = {3 /*family*/, best, vec ? 1 : 0, (int)c.x.size(), (int)c.y.size(), (int)c.r.size()};
   for (const auto& p : c.x) { key.push_back(p.l); key.push_back(p.n); }

@@ -1,0 +1,642 @@
+// Backward Clebsch-Gordan product on the 5th-generation tensor cores (tcgen05 + tensor memory), for channel
+// counts that are multiples of 32.  Same mathematics as cg_bwd.cu; replaces the same reference code
+// (cuda/SO3part_addCGproduct_back0.cu:32-294, cuda/SO3part_addCGproduct_back1.cu:32-175 and the loops
+// Gvec::add_CGproduct_back0 / _back1, core/Gvec.hpp:323-345 of GElib).
+//
+// Formulation.  A slab is one row m of one triple (l1,l2)->l restricted to a 32 x 32 channel tile of g:
+// G[n1][n2], 8 KB.  For the slab, against ALL rows m2 of y_l2 and ALL rows m1 of x_l1,
+//     P[n1][(m2,part)] = sum_{n2,c} G_c[n1][n2] By[(n2,c)][(m2,part)]      (part = re | im of g conj(y))
+//     Q[n2][(m1,part)] = sum_{n1,c} G_c[n1][n2] Bx[(n1,c)][(m1,part)]
+// with By[(n2,re)] = (y_r | -y_i), By[(n2,im)] = (y_i | y_r) and the same for x, are real GEMMs with K = 64.  Four
+// slabs that share (l1,l2) and the tile are stacked to M = 128 rows; N = 16 or 32 covers the 2(2l+1) rows of
+// the other operand.  Only the band |m - m2| <= l1 (resp. |m - m1| <= l2) of the result is used: the
+// epilogue scales those columns by the Clebsch-Gordan coefficient and adds them to the gradient rows,
+//     xg[m1][n1] += C(m1, m-m1) P[n1][m2 = m-m1],      yg[m2][n2] += C(m-m2, m2) Q[n2][m1 = m-m2].
+// The MMAs run as tcgen05.mma kind::tf32 with the 3xTF32 split (a = a_hi + a_lo with a_hi the upper 19 bits;
+// a_lo b_hi + a_hi b_lo + a_hi b_hi, FP32 accumulation in tensor memory), which keeps FP32-level accuracy.
+//
+// Data movement per CTA (one cell).  At start the x and y rows are written to shared memory once, already split
+// and in the K-major core-matrix layout the B operand descriptor wants (rows 2*mi and 2*mi+1 = the two parts).
+// Eight worker warps each own one slab at a time: cp.async brings it into the warp's 8 KB ring slot
+// (16-byte chunks XOR-swizzled by row), the warp reads it row-per-lane, splits it and stores it to tensor memory
+// as the A operand of the P product (lane = n1, columns = (n2,c)), later column-per-lane for the Q product
+// (lane = n2, columns = (n1,c)); A never passes through shared memory again.  Warps 0-3 and 4-7 form two sets
+// with their own tensor-memory columns (A 128, P 32, Q 32) and their own issuing warp (8, 9), so that one set's
+// MMAs overlap the other's loads, splits and epilogues.  The epilogue reads the accumulator row of its lane with
+// tcgen05.ld and adds into gradient rows in shared memory with shared-memory atomics; the rows go to global
+// memory once at the end.  Gradients are reproducible to rounding, not bitwise.
+//
+// Every wait on an mbarrier is bounded; on a timeout the kernel records it in a host-mapped status word,
+// leaves its loops, frees its tensor memory and returns, and the next call reports the failure.
+#include <algorithm>
+#include <cstdint>
+#include <map>
+#include <mutex>
+
+#include "plan.h"
+
+namespace gelib_b200 {
+
+namespace {
+
+constexpr int kWorkers = 16;          // worker warps: two sets of four slabs, two warps per slab
+constexpr int kThreads = 32 * (kWorkers + 2);
+constexpr int kSlots = 8;             // ring slots (one slab each)
+constexpr int kSlabBytes = 32 * 32 * 8;
+constexpr int kHeaderBytes = 768;     // mbarriers, tensor-memory base, cell offsets, g row pointers
+constexpr int kRec = 6;               // int4 per group record
+constexpr int kWaitLimit = 256;        // tries per wait, each parked for at most kSuspendNs
+constexpr uint32_t kSuspendNs = 1000000;
+
+struct TcArgs {
+  PartView x[kMaxParts], y[kMaxParts], g[kMaxParts], xg[kMaxParts], yg[kMaxParts];
+  int xacc[kMaxParts], yacc[kMaxParts];  // float offsets of the gradient rows inside the accumulator block
+  int xbt[kMaxParts], ybt[kMaxParts];    // byte offsets of the operand tables inside the table block
+  int xR[kMaxParts], yR[kMaxParts];      // table rows per part: 2(2l+1) rounded up to 8
+  int nx, ny, ng;
+  int bt_bytes, acc_floats;
+  CellGrid cg;
+  const float* coeffs;
+  // six int4 per group of up to four slabs (nothing in the loops indexes the parameter arrays):
+  //   {xi | yi<<4 | l1<<8 | l2<<16, a0 | b0<<16, n1 | n2<<16 (channels of the x and y part), xacc | yacc<<16}
+  //   {byte offset of the y table of the tile, its rows, byte offset of the x table of the tile, its rows}
+  //   4 x {ri | valid<<8, l | (m+l)<<8, channel offset of the tile inside part ri, coefficient index}
+  const int4* groups;
+  int ngroups;
+  int offs_extra;
+  int x_atomic, y_atomic;
+  int* status;  // host-mapped: set to 1 when a wait timed out
+};
+
+// ---- PTX wrappers ----------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("{ .reg .b64 t; mbarrier.arrive.shared::cta.b64 t, [%0]; }" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait for the phase with the given parity; false on timeout.  The suspend-time hint lets the hardware
+// park the warp until the phase completes instead of polling the shared-memory pipe that everybody else needs.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t a = smem_u32(bar);
+  for (int i = 0; i < kWaitLimit; i++) {
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok)
+                 : "r"(a), "r"(parity), "r"(kSuspendNs)
+                 : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[tmem] * B[smem descriptor]; issued by one elected lane of a converged warp.
+__device__ __forceinline__ void mma_tf32_ts(uint32_t d, uint32_t a, uint64_t bdesc, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{ .reg .pred P, Q; elect.sync _|P, 0xffffffff; setp.ne.b32 Q, %4, 0;\n"
+      "@P tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, Q; }" ::"r"(d), "r"(a), "l"(bdesc), "r"(idesc),
+      "r"((uint32_t)accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier when all MMAs issued so far by this thread have completed.
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile(
+      "{ .reg .pred P; elect.sync _|P, 0xffffffff;\n"
+      "@P tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0]; }" ::"r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+__device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) {
+  hi = __float_as_uint(v) & 0xffffe000u;
+  lo = __float_as_uint(v - __uint_as_float(hi));
+}
+
+// Splits 16 values and stores them to columns [col, col+16) of the hi block and of the lo block (64 columns on).
+__device__ __forceinline__ void split_store16(uint32_t tA, int col, const float (&v)[16]) {
+  uint32_t hi[16], lo[16];
+#pragma unroll
+  for (int i = 0; i < 16; i++) split_tf32(v[i], hi[i], lo[i]);
+  tmem_st16(tA + col, hi);
+  tmem_st16(tA + 64 + col, lo);
+}
+
+// ---- kernel pieces ---------------------------------------------------------------------------------------------
+
+// Everything a worker needs for its slab of one group, kept packed as loaded (registers are scarce here).
+struct Work {
+  int4 h;      // {xi | yi<<4 | l1<<8 | l2<<16, a0 | b0<<16, n1 | n2<<16, xacc | yacc<<16}
+  int4 r;      // {ri | valid<<8, l | (m+l)<<8, channel offset of the tile inside part ri, coefficient index}
+  float cvec;  // band coefficient j of the slab's row in lane j (at most 15 entries)
+  __device__ __forceinline__ int l1() const { return (h.x >> 8) & 0xff; }
+  __device__ __forceinline__ int l2() const { return (h.x >> 16) & 0xff; }
+  __device__ __forceinline__ int a0() const { return h.y & 0xffff; }
+  __device__ __forceinline__ int b0() const { return (h.y >> 16) & 0xffff; }
+  __device__ __forceinline__ int n1() const { return h.z & 0xffff; }
+  __device__ __forceinline__ int n2() const { return (h.z >> 16) & 0xffff; }
+  __device__ __forceinline__ int xacc() const { return h.w & 0xffff; }
+  __device__ __forceinline__ int yacc() const { return (h.w >> 16) & 0xffff; }
+  __device__ __forceinline__ int ri() const { return r.x & 0xff; }
+  __device__ __forceinline__ bool valid() const { return (r.x >> 8) & 1; }
+  __device__ __forceinline__ int m() const { return (r.y >> 8) - (r.y & 0xff); }
+};
+
+// The records are fetched two groups ahead (load_records) and completed one group ahead (load_coeffs), so that
+// nothing in the loop waits for a load it has just issued.
+__device__ __forceinline__ void load_records(const TcArgs& A, int g, int q, Work& w) {
+  w.h = __ldg(&A.groups[kRec * g]);
+  w.r = __ldg(&A.groups[kRec * g + 2 + q]);
+}
+__device__ __forceinline__ void load_coeffs(const TcArgs& A, Work& w, int lane) {
+  w.cvec = 0.f;
+  if (w.valid()) {
+    const int K = min(w.l1(), w.m() + w.l2()) - max(-w.l1(), w.m() - w.l2()) + 1;
+    if (lane < K) w.cvec = __ldg(A.coeffs + w.r.w + lane);
+  }
+}
+
+__device__ __noinline__ void fill_offsets(long long* dst, const PartView* parts, int nparts, const CellGrid& cg, long long cell) {
+  for (int p = threadIdx.x; p < nparts; p += blockDim.x) dst[p] = cell_offset(parts[p], cg, cell);
+}
+
+// Writes the rows of every part of one vector as split B-operand tables.  Table of (part, 32-channel tile):
+// a hi block and a lo block of [16 k-chunks][R rows][4 floats] each; row 2*mi holds (v_r, v_i) pairs, row 2*mi+1
+// (-v_i, v_r) pairs of row mi, so that one k-chunk is two complex channels.
+__device__ __noinline__ void stage_tables(unsigned char* bt, const PartView* parts, const int* off, const int* Rs,
+                                             int nparts, const CellGrid& cg, long long cell) {
+  for (int i = 0; i < nparts; i++) {
+    const PartView& p = parts[i];
+    const float* src = p.base + cell_offset(p, cg, cell);
+    const int T = p.n >> 5, R = Rs[i];
+    const int total = (2 * p.l + 1) * T * 16;
+    for (int e = threadIdx.x; e < total; e += blockDim.x) {
+      const int kc = e & 15, t = (e >> 4) % T, mi = (e >> 4) / T;
+      const float4 v = __ldg(reinterpret_cast<const float4*>(src + (long long)mi * p.sm + 2 * (32 * t + 2 * kc)));
+      const float re[4] = {v.x, v.y, v.z, v.w}, im[4] = {-v.y, v.x, -v.w, v.z};
+      uint32_t rh[4], rl[4], ih[4], il[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        split_tf32(re[k], rh[k], rl[k]);
+        split_tf32(im[k], ih[k], il[k]);
+      }
+      unsigned char* tile = bt + off[i] + t * (512 * R);
+      uint4* hi = reinterpret_cast<uint4*>(tile + (kc * R + 2 * mi) * 16);
+      uint4* lo = reinterpret_cast<uint4*>(tile + 256 * R + (kc * R + 2 * mi) * 16);
+      hi[0] = make_uint4(rh[0], rh[1], rh[2], rh[3]);
+      hi[1] = make_uint4(ih[0], ih[1], ih[2], ih[3]);
+      lo[0] = make_uint4(rl[0], rl[1], rl[2], rl[3]);
+      lo[1] = make_uint4(il[0], il[1], il[2], il[3]);
+    }
+  }
+}
+
+// The 24 MMAs of one product of a group: D[128 x N] = A_lo B_hi + A_hi B_lo + A_hi B_hi over K = 64 in steps of 8.
+// tA: tensor-memory column of the set's A block (hi at +0, lo at +64); table: shared address of the B table.
+__device__ __forceinline__ void issue_product(uint32_t tA, uint32_t tD, uint32_t table, int R) {
+  const uint32_t N = R <= 16 ? 16u : 32u;
+  // instruction descriptor: D = F32, A = B = TF32, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((N >> 3) << 17) | ((128u >> 4) << 24);
+  // shared-memory descriptor, no swizzle, K-major: start >> 4, leading (k-chunk) offset R*16 B, stride (8-row
+  // group) offset 128 B, descriptor version 1
+  const uint64_t fixed = ((uint64_t)R << 16) | (8ull << 32) | (1ull << 46);
+  const uint64_t dhi = fixed | ((table >> 4) & 0x3fffu), dlo = fixed | (((table + 256u * R) >> 4) & 0x3fffu);
+  const uint64_t kstep = 2ull * R;  // two k-chunks per MMA, in 16-byte units
+#pragma unroll
+  for (int term = 0; term < 3; term++) {
+    const uint32_t a = term == 0 ? tA + 64 : tA;  // a_lo b_hi, a_hi b_lo, a_hi b_hi: smallest terms first
+    const uint64_t b = term == 1 ? dlo : dhi;
+#pragma unroll
+    for (int ks = 0; ks < 8; ks++) mma_tf32_ts(tD, a + 8 * ks, b + ks * kstep, idesc, (term | ks) != 0);
+  }
+}
+
+// Adds the band of one accumulator row to the gradient rows.  The accumulator of the lane's channel holds, for
+// every row index idx of the other operand (lb = its l), the complex sum in columns 2 idx, 2 idx + 1.
+//   FOR_X: idx <-> m2, target row m1 = m - m2 of x;   else: idx <-> m1, target row m2 = m - m1 of y.
+// cvec: the row's band coefficients, entry j in lane j.
+// The additions are 64-bit compare-and-swap updates of the complex gradient entries, four band entries at a
+// time (all accumulator reads, all loads, all swaps, then retries of the few that lost a race) so that their
+// latencies overlap; shared memory has no native float add, and an atomicAdd per float would serialise a
+// loop per entry.
+template <bool FOR_X>
+__device__ __forceinline__ void epilogue(uint32_t tD, float* accrows, int ntot, int ch, int m, int l1, int l2,
+                                         float cvec) {
+  const int lo = max(-l1, m - l2), hi = min(l1, m + l2);
+  const int lb = FOR_X ? l2 : l1, lt = FOR_X ? l1 : l2;
+  const int i0 = FOR_X ? (m - hi + lb) : (lo + lb), i1 = FOR_X ? (m - lo + lb) : (hi + lb);  // the band of idx
+  unsigned long long* base = reinterpret_cast<unsigned long long*>(accrows) + ch;
+  auto pack = [](float re, float im) { return ((unsigned long long)__float_as_uint(im) << 32) | __float_as_uint(re); };
+  for (int j0 = i0; j0 <= i1; j0 += 4) {
+    uint32_t dv[8];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int idx = min(j0 + i, i1);
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0,%1}, [%2];" : "=r"(dv[2 * i]), "=r"(dv[2 * i + 1]) : "r"(tD + 2 * idx) : "memory");
+    }
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(dv[0]), "+r"(dv[1]), "+r"(dv[2]), "+r"(dv[3]), "+r"(dv[4]), "+r"(dv[5]), "+r"(dv[6]), "+r"(dv[7])::"memory");
+    unsigned long long oldv[4], got[4];
+    unsigned long long* ptr[4];
+    float2 add[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int idx = min(j0 + i, i1);
+      const int mb = idx - lb, m1 = FOR_X ? m - mb : mb, mt = m - mb;
+      const float c = __shfl_sync(0xffffffffu, cvec, m1 - lo);
+      add[i] = make_float2(c * __uint_as_float(dv[2 * i]), c * __uint_as_float(dv[2 * i + 1]));
+      ptr[i] = base + (mt + lt) * ntot;
+      oldv[i] = *ptr[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+      if (j0 + i <= i1)
+        got[i] = atomicCAS(ptr[i], oldv[i],
+                           pack(__uint_as_float((uint32_t)oldv[i]) + add[i].x, __uint_as_float((uint32_t)(oldv[i] >> 32)) + add[i].y));
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+      if (j0 + i <= i1)
+        while (got[i] != oldv[i]) {  // another warp updated the entry in between: redo on its value
+          oldv[i] = got[i];
+          got[i] = atomicCAS(ptr[i], oldv[i],
+                             pack(__uint_as_float((uint32_t)oldv[i]) + add[i].x, __uint_as_float((uint32_t)(oldv[i] >> 32)) + add[i].y));
+        }
+  }
+}
+
+__device__ __noinline__ void flush_rows(const float* acc, const PartView* out, const long long* cell_off,
+                                           const int* off, int nparts, bool atomic) {
+  for (int i = 0; i < nparts; i++) {
+    const PartView& p = out[i];
+    const int n = p.n, total = (2 * p.l + 1) * n;
+    for (int e = threadIdx.x; e < total; e += blockDim.x) {
+      const int row = e / n, ch = e - row * n;
+      const float2 v = *reinterpret_cast<const float2*>(acc + off[i] + 2 * e);
+      float* dst = p.base + cell_off[i] + (long long)row * p.sm + 2 * ch;
+      if (atomic) {
+        atomicAdd(dst, v.x);
+        atomicAdd(dst + 1, v.y);
+      } else {
+        float2 o = *reinterpret_cast<float2*>(dst);
+        o.x += v.x;
+        o.y += v.y;
+        *reinterpret_cast<float2*>(dst) = o;
+      }
+    }
+  }
+}
+
+// ---- the kernel ------------------------------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_constant__ TcArgs A) {
+  extern __shared__ __align__(128) unsigned char sm[];
+  uint64_t* aready = reinterpret_cast<uint64_t*>(sm);  // [2] A operand stored (4 worker warps arrive)
+  uint64_t* mdone_x = aready + 2;                      // [2] MMAs of the P product complete
+  uint64_t* mdone_y = aready + 4;                      // [2] MMAs of the Q product complete
+  uint32_t* tbase_s = reinterpret_cast<uint32_t*>(sm + 48);
+  long long* goff = reinterpret_cast<long long*>(sm + 64);
+  long long* xgoff = goff + kMaxParts;
+  long long* ygoff = xgoff + kMaxParts;
+  const float** gptr = reinterpret_cast<const float**>(ygoff + kMaxParts);  // g part base of this cell
+  long long* gsm = reinterpret_cast<long long*>(gptr + kMaxParts);          // g row stride
+  unsigned char* bt = sm + kHeaderBytes;
+  float* acc = reinterpret_cast<float*>(bt + A.bt_bytes);
+  unsigned char* ring = reinterpret_cast<unsigned char*>(acc + A.acc_floats);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long cell = blockIdx.x;
+
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tbase_s)), "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (threadIdx.x == 32) {
+    for (int s = 0; s < 2; s++) {
+      mbar_init(aready + s, 8);
+      mbar_init(mdone_x + s, 1);
+      mbar_init(mdone_y + s, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  fill_offsets(goff, A.g, A.ng, A.cg, cell);
+  fill_offsets(xgoff, A.xg, A.nx, A.cg, cell);
+  fill_offsets(ygoff, A.yg, A.ny, A.cg, cell);
+  {
+    float4* z = reinterpret_cast<float4*>(bt);
+    const int n16 = (A.bt_bytes + 4 * A.acc_floats) >> 4;
+    for (int e = threadIdx.x; e < n16; e += blockDim.x) z[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  __syncthreads();
+  if (threadIdx.x < A.ng) {
+    gptr[threadIdx.x] = A.g[threadIdx.x].base + goff[threadIdx.x] + 2LL * A.offs_extra;
+    gsm[threadIdx.x] = A.g[threadIdx.x].sm;
+  }
+  stage_tables(bt, A.y, A.ybt, A.yR, A.ny, A.cg, cell);
+  stage_tables(bt, A.x, A.xbt, A.xR, A.nx, A.cg, cell);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // tables are read by the tensor core (async proxy)
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = *tbase_s;
+
+  if (warp < kWorkers) {
+    // ------------------------------------------------ worker: half of one slab of every group of its set
+    const int h = warp >> 3, s = (warp >> 2) & 1, q = warp & 3;
+    const uint32_t lanes = (uint32_t)(32 * q) << 16;
+    const uint32_t tA = tbase + 256 * s + lanes, tDX = tA + 128, tDY = tA + 160;
+    unsigned char* slot = ring + (4 * s + q) * kSlabBytes;
+    const uint32_t slot_u32 = smem_u32(slot);
+    const int pair_bar = 1 + 4 * s + q;  // named barrier of the two warps that share the slab
+    const int ngs = (A.ngroups - s + 1) >> 1;
+    uint32_t par_x = 0, par_y = 0;
+    bool ok = true;
+    // cp.async chunk e = (8 h + i) * 32 + lane of the slab: row 2 (8 h + i) + (lane >> 4), 16-byte chunk lane & 15
+    const int pf_row0 = 16 * h + (lane >> 4), pf_c = (lane & 15) ^ (lane >> 4);
+
+    auto prefetch = [&](const Work& w) {  // this warp's half of the slab into the ring slot
+      if (w.valid()) {
+        const int n2tot = w.n2();
+        const float* src = gptr[w.ri()] + (long long)(w.r.y >> 8) * gsm[w.ri()] + 2LL * w.r.z +
+                           (long long)pf_row0 * 2 * n2tot + 4 * (lane & 15);
+        const uint32_t dst = slot_u32 + pf_row0 * 256;
+        const long long step = 4LL * n2tot;  // two rows, in floats
+#pragma unroll
+        for (int i = 0; i < 8; i++)  // row & 15 = (2 i + (lane >> 4)) & 15 (16 h drops out): chunk ^ row = pf_c ^ 2 i
+          cp_async16(dst + i * 512 + ((pf_c ^ (2 * i)) << 4), src + i * step);
+      }
+      cp_async_commit();
+    };
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory"); };
+
+    Work cur{}, prev{}, next{}, after{};  // `after`: records only
+    if (ngs > 0) {
+      load_records(A, s, q, next);
+      load_coeffs(A, next, lane);
+      prefetch(next);
+      if (ngs > 1) load_records(A, s + 2, q, after);
+    }
+    bool have_prev = false;
+
+    // After a timeout (ok == false) the loop keeps its named barriers and arrivals but skips the work and the
+    // waits, so that the two warps of a pair never wait for each other in vain.
+    for (int k = 0; k < ngs; k++) {
+      cur = next;
+      if (k + 1 < ngs) {
+        next = after;
+        load_coeffs(A, next, lane);
+      }
+      if (k + 2 < ngs) load_records(A, s + 2 * (k + 2), q, after);
+
+      // 1. A operand of the P product: lane = row n1 of the slab, this warp's 32 of the 64 columns (n2, re/im)
+      cp_async_wait_all();
+      pair_sync();
+      if (cur.valid()) {
+#pragma unroll
+        for (int c4 = 0; c4 < 2; c4++) {
+          float v[16];
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const int c = 8 * h + 4 * c4 + i;
+            const float4 f = *reinterpret_cast<const float4*>(slot + lane * 256 + ((c ^ (lane & 15)) << 4));
+            v[4 * i] = f.x, v[4 * i + 1] = f.y, v[4 * i + 2] = f.z, v[4 * i + 3] = f.w;
+          }
+          split_store16(tA, 32 * h + 16 * c4, v);
+        }
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(aready + s);
+
+      // 2. the upper warps add the Q result of the previous group (overlaps this group's P MMAs)
+      if (ok && h == 1 && have_prev && prev.valid())
+        epilogue<false>(tDY, acc + prev.yacc(), prev.n2(), prev.b0() + lane, prev.m(), prev.l1(), prev.l2(), prev.cvec);
+
+      // 3. A operand of the Q product, once the P MMAs have consumed the previous contents: the slab
+      //    column-per-lane (lane = n2), this warp's 16 of the 32 rows n1 as columns (n1, re/im)
+      if (ok) ok = mbar_wait(mdone_x + s, par_x);
+      par_x ^= 1;
+      tc_fence_after();
+      if (ok && cur.valid()) {
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+          float v[16];
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const int n1 = 16 * h + 8 * j + i;
+            const float2 f = *reinterpret_cast<const float2*>(slot + n1 * 256 + (((lane >> 1) ^ (n1 & 15)) << 4) + ((lane & 1) << 3));
+            v[2 * i] = f.x, v[2 * i + 1] = f.y;
+          }
+          split_store16(tA, 32 * h + 16 * j, v);
+        }
+      }
+      pair_sync();  // both warps have read the slot: refill it with the next slab
+      if (k + 1 < ngs) prefetch(next);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(aready + s);
+
+      // 4. the lower warps add the P result (overlaps the Q MMAs)
+      if (ok && h == 0 && cur.valid())
+        epilogue<true>(tDX, acc + cur.xacc(), cur.n1(), cur.a0() + lane, cur.m(), cur.l1(), cur.l2(), cur.cvec);
+
+      // 5. the A block is free again when the Q MMAs are done
+      if (ok) ok = mbar_wait(mdone_y + s, par_y);
+      par_y ^= 1;
+      tc_fence_after();
+      prev = cur, have_prev = true;
+    }
+    if (ok && h == 1 && have_prev && prev.valid())
+      epilogue<false>(tDY, acc + prev.yacc(), prev.n2(), prev.b0() + lane, prev.m(), prev.l1(), prev.l2(), prev.cvec);
+    cp_async_wait_all();
+    if (!ok && lane == 0) *A.status = 1;
+  } else {
+    // ------------------------------------------------ issuer of set s: 2 x 24 MMAs per group
+    const int s = warp - kWorkers;
+    const uint32_t tA = tbase + 256 * s, tDX = tA + 128, tDY = tA + 160;
+    const uint32_t bt_u32 = smem_u32(bt);
+    const int ngs = (A.ngroups - s + 1) >> 1;
+    uint32_t par_a = 0;
+    bool ok = true;
+    int4 hn = ngs > 0 ? __ldg(&A.groups[kRec * s + 1]) : make_int4(0, 0, 0, 0);
+    for (int k = 0; k < ngs && ok; k++) {
+      const int4 h = hn;  // {y table offset, y rows, x table offset, x rows}
+      if (k + 1 < ngs) hn = __ldg(&A.groups[kRec * (s + 2 * (k + 1)) + 1]);
+      ok = mbar_wait(aready + s, par_a);
+      par_a ^= 1;
+      if (!ok) break;
+      tc_fence_after();
+      issue_product(tA, tDX, bt_u32 + h.x, h.y);
+      mma_commit(mdone_x + s);
+      ok = mbar_wait(aready + s, par_a);
+      par_a ^= 1;
+      if (!ok) break;
+      tc_fence_after();
+      issue_product(tA, tDY, bt_u32 + h.z, h.w);
+      mma_commit(mdone_y + s);
+    }
+    if (!ok && lane == 0) *A.status = 1;
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  flush_rows(acc, A.xg, xgoff, A.xacc, A.nx, A.x_atomic != 0);
+  flush_rows(acc, A.yg, ygoff, A.yacc, A.ny, A.y_atomic != 0);
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(512u) : "memory");
+  }
+}
+
+}  // namespace
+
+// ---- launcher --------------------------------------------------------------------------------------------------
+
+namespace {
+
+int* status_word() {  // one host-mapped word for the process; kernels of any device can set it
+  static int* w = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess) {
+      w = static_cast<int*>(p);
+      *w = 0;
+    } else {
+      cudaGetLastError();
+    }
+  });
+  return w;
+}
+
+inline int round_up(int v, int q) { return (v + q - 1) / q * q; }
+
+}  // namespace
+
+// Returns -1 when the call does not qualify (the caller then takes the SIMT kernels).
+int launch_cg_bwd_tc(const VecCall& c, cudaStream_t s) {
+  static const char* fn = "SO3vec_addCGproduct_back";
+  if (!c.vec_ok || c.xg.empty() || c.yg.empty()) return -1;
+  if (c.x.size() > 15 || c.y.size() > 15 || c.r.size() > 15) return -1;
+  for (const auto& p : c.x) if (p.n % 32 || p.l > 7 || p.n > 32768) return -1;
+  for (const auto& p : c.y) if (p.n % 32 || p.l > 7 || p.n > 32768) return -1;
+  for (const auto& p : c.r) if (p.l > 127) return -1;
+  int dev = 0, cc_major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  if (cc_major != 10) return -1;
+  int* status = status_word();
+  if (!status) return -1;
+  if (*status != 0) {
+    *status = 0;
+    set_error(std::string(fn) + ": a tensor-core backward kernel gave up waiting on an mbarrier; its gradients are incomplete.");
+    return GELIB_CUDA_ERROR;
+  }
+
+  TcArgs a;
+  int bt = 0, acc = 0;
+  for (size_t i = 0; i < c.y.size(); i++) {
+    a.y[i] = c.y[i];
+    a.yg[i] = c.yg[i];
+    a.yR[i] = round_up(2 * (2 * c.y[i].l + 1), 8);
+    a.ybt[i] = bt;
+    bt += (c.y[i].n / 32) * 512 * a.yR[i];
+    a.yacc[i] = acc;
+    acc += 2 * (2 * c.y[i].l + 1) * c.y[i].n;
+  }
+  for (size_t i = 0; i < c.x.size(); i++) {
+    a.x[i] = c.x[i];
+    a.xg[i] = c.xg[i];
+    a.xR[i] = round_up(2 * (2 * c.x[i].l + 1), 8);
+    a.xbt[i] = bt;
+    bt += (c.x[i].n / 32) * 512 * a.xR[i];
+    a.xacc[i] = acc;
+    acc += 2 * (2 * c.x[i].l + 1) * c.x[i].n;
+  }
+  bt += 512;  // an N = 32 read of a table with fewer rows runs into the next k-chunk: keep the last one in bounds
+  for (size_t i = 0; i < c.r.size(); i++) a.g[i] = c.r[i];
+  a.nx = (int)c.x.size();
+  a.ny = (int)c.y.size();
+  a.ng = (int)c.r.size();
+  a.bt_bytes = bt;
+  a.acc_floats = round_up(acc, 32);
+  const size_t smem = (size_t)kHeaderBytes + bt + 4 * (size_t)a.acc_floats + (size_t)kSlots * kSlabBytes;
+  if (smem > 227 * 1024 || 4 * (size_t)a.acc_floats > 0xffff * 4) return -1;
+
+  std::vector<int> key = {7 /*family*/, (int)c.x.size(), (int)c.y.size(), (int)c.r.size()};
+  for (const auto& p : c.x) { key.push_back(p.l); key.push_back(p.n); }
+  for (const auto& p : c.y) { key.push_back(p.l); key.push_back(p.n); }
+  for (const auto& p : c.r) key.push_back(p.l);
+  const auto xs = sig_of(c.x), ys = sig_of(c.y), rs = sig_of(c.r);
+  const int *xacc = a.xacc, *yacc = a.yacc, *xbt = a.xbt, *ybt = a.ybt, *xR = a.xR, *yR = a.yR;
+  DevicePlan* plan = get_plan(key, [&](DevicePlan& p) {
+    build_schedule(xs, ys, rs, false, true, &p.sched);
+    // slabs keyed by (xi, yi, a0, b0): they share both B operands
+    std::map<std::vector<int>, std::vector<int4>> buckets;
+    for (const Triple& t : p.sched.triples) {
+      int cpos = t.coff;
+      for (int m = -t.l; m <= t.l; m++) {
+        const int lo = std::max<int>(-t.l1, m - t.l2), hi = std::min<int>(t.l1, m + t.l2);
+        for (int a0 = 0; a0 < xs[t.xi].n; a0 += 32)
+          for (int b0 = 0; b0 < ys[t.yi].n; b0 += 32)
+            buckets[{t.xi, t.yi, a0, b0}].push_back(
+                make_int4(t.ri | (1 << 8), t.l | ((m + t.l) << 8), t.offs + a0 * ys[t.yi].n + b0, cpos));
+        cpos += hi - lo + 1;
+      }
+    }
+    for (const auto& kv : buckets) {
+      const auto& v = kv.second;
+      const int xi = kv.first[0], yi = kv.first[1], a0 = kv.first[2], b0 = kv.first[3];
+      for (size_t i = 0; i < v.size(); i += 4) {
+        const int ns = (int)std::min<size_t>(4, v.size() - i);
+        p.h_items.push_back(make_int4(xi | (yi << 4) | (xs[xi].l << 8) | (ys[yi].l << 16), a0 | (b0 << 16),
+                                      xs[xi].n | (ys[yi].n << 16), xacc[xi] | (yacc[yi] << 16)));
+        p.h_items.push_back(make_int4(ybt[yi] + (b0 >> 5) * 512 * yR[yi], yR[yi], xbt[xi] + (a0 >> 5) * 512 * xR[xi], xR[xi]));
+        for (int j = 0; j < 4; j++) p.h_items.push_back(j < ns ? v[i + j] : make_int4(0, 0, 0, 0));
+      }
+    }
+  });
+  if (!plan) return GELIB_CUDA_ERROR;
+  if (plan->nitems == 0 || c.cg.ncells == 0) return GELIB_OK;
+  if (c.cg.ncells > 0x7fffffffLL) return fail(GELIB_SKIPPED, fn, "number of cells exceeds 2^31-1");
+
+  a.cg = c.cg;
+  a.coeffs = plan->coeffs;
+  a.groups = plan->items;
+  a.ngroups = plan->nitems / kRec;
+  a.offs_extra = c.offs_extra;
+  a.x_atomic = c.xg_bcast ? 1 : 0;
+  a.y_atomic = c.yg_bcast ? 1 : 0;
+  a.status = status;  // unified addressing: the host pointer of mapped memory is valid on the device
+  cudaError_t e = cudaFuncSetAttribute(cg_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e == cudaSuccess) {
+    cg_bwd_tc_kernel<<<(unsigned)c.cg.ncells, kThreads, smem, s>>>(a);
+    e = cudaGetLastError();
+  }
+  if (e != cudaSuccess) return check_cuda(e, fn, "tensor-core backward kernel launch");
+  count_launch();
+  return GELIB_OK;
+}
+
+}  // namespace gelib_b200

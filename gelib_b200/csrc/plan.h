@@ -30,6 +30,7 @@ DevicePlan* get_plan(const std::vector<int>& key, const std::function<void(Devic
 // Kernel families (each returns a status code).
 int launch_cg_fwd(const VecCall& c, cudaStream_t s);
 int launch_cg_bwd(const VecCall& c, cudaStream_t s);
+int launch_cg_bwd_tc(const VecCall& c, cudaStream_t s);  // tcgen05 kernel; -1 when the call does not qualify
 int launch_cg_narrow_bwd(const VecCall& c, cudaStream_t s);
 int launch_cg_narrow_fwd(const VecCall& c, cudaStream_t s);  // x with at most 4 channels; -1 when the call does not qualify
 int launch_cg_strided(const VecCall& c, int mode, cudaStream_t s);  // mode 0 fwd, 1 back0, 2 back1
