@@ -30,6 +30,7 @@
 // leaves its loops, frees its tensor memory and returns, and the next call reports the failure.
 #include <algorithm>
 #include <cstdint>
+#include <cstring>
 #include <map>
 #include <mutex>
 
@@ -40,11 +41,11 @@ namespace gelib_b200 {
 namespace {
 
 constexpr int kWorkers = 16;          // worker warps: two sets of four slabs, two warps per slab
-constexpr int kThreads = 32 * (kWorkers + 2);
+constexpr int kThreads = 32 * kWorkers;
 constexpr int kSlots = 8;             // ring slots (one slab each)
 constexpr int kSlabBytes = 32 * 32 * 8;
-constexpr int kHeaderBytes = 768;     // mbarriers, tensor-memory base, cell offsets, g row pointers
-constexpr int kRec = 6;               // int4 per group record
+constexpr int kHeaderBytes = 896;     // mbarriers, tensor-memory base, cell offsets, g row pointers
+constexpr int kRec = 22;              // int4 per group record
 constexpr int kWaitLimit = 256;        // tries per wait, each parked for at most kSuspendNs
 constexpr uint32_t kSuspendNs = 1000000;
 
@@ -61,6 +62,7 @@ struct TcArgs {
   //   {xi | yi<<4 | l1<<8 | l2<<16, a0 | b0<<16, n1 | n2<<16 (channels of the x and y part), xacc | yacc<<16}
   //   {byte offset of the y table of the tile, its rows, byte offset of the x table of the tile, its rows}
   //   4 x {ri | valid<<8, l | (m+l)<<8, channel offset of the tile inside part ri, coefficient index}
+  //   4 x 16 floats: the band coefficients of the slab's row, zero-padded
   const int4* groups;
   int ngroups;
   int offs_extra;
@@ -75,9 +77,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("{ .reg .b64 t; mbarrier.arrive.shared::cta.b64 t, [%0]; }" ::"r"(smem_u32(bar)) : "memory");
-}
 // Bounded wait for the phase with the given parity; false on timeout.  The suspend-time hint lets the hardware
 // park the warp until the phase completes instead of polling the shared-memory pipe that everybody else needs.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
@@ -91,6 +90,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (ok) return true;
   }
   return false;
+}
+// Counts one arrival; true in every lane of the warp that arrives eighth.
+__device__ __forceinline__ bool count_event(int* counter) {
+  int old = 0;
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) {
+    __threadfence_block();
+    old = atomicAdd(counter, 1);
+    __threadfence_block();
+  }
+  old = __shfl_sync(0xffffffffu, old, 0);
+  return (old & 7) == 7;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -110,13 +121,6 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
       "@P tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0]; }" ::"r"(smem_u32(bar))
       : "memory");
 }
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -130,13 +134,20 @@ __device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) 
   lo = __float_as_uint(v - __uint_as_float(hi));
 }
 
-// Splits 16 values and stores them to columns [col, col+16) of the hi block and of the lo block (64 columns on).
-__device__ __forceinline__ void split_store16(uint32_t tA, int col, const float (&v)[16]) {
-  uint32_t hi[16], lo[16];
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+               "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
+// Splits 8 values and stores them to columns [col, col+8) of the hi block and of the lo block (64 columns on).
+// Eight at a time keeps the live registers low: the kernel runs 18 warps at 96 registers per thread.
+__device__ __forceinline__ void split_store8(uint32_t tA, int col, const float (&v)[8]) {
+  uint32_t hi[8], lo[8];
 #pragma unroll
-  for (int i = 0; i < 16; i++) split_tf32(v[i], hi[i], lo[i]);
-  tmem_st16(tA + col, hi);
-  tmem_st16(tA + 64 + col, lo);
+  for (int i = 0; i < 8; i++) split_tf32(v[i], hi[i], lo[i]);
+  tmem_st8(tA + col, hi);
+  tmem_st8(tA + 64 + col, lo);
 }
 
 // ---- kernel pieces ---------------------------------------------------------------------------------------------
@@ -145,6 +156,7 @@ __device__ __forceinline__ void split_store16(uint32_t tA, int col, const float 
 struct Work {
   int4 h;      // {xi | yi<<4 | l1<<8 | l2<<16, a0 | b0<<16, n1 | n2<<16, xacc | yacc<<16}
   int4 r;      // {ri | valid<<8, l | (m+l)<<8, channel offset of the tile inside part ri, coefficient index}
+  int4 t;      // {y table byte offset, y rows, x table byte offset, x rows}: for the warp that issues the MMAs
   float cvec;  // band coefficient j of the slab's row in lane j (at most 15 entries)
   __device__ __forceinline__ int l1() const { return (h.x >> 8) & 0xff; }
   __device__ __forceinline__ int l2() const { return (h.x >> 16) & 0xff; }
@@ -159,18 +171,12 @@ struct Work {
   __device__ __forceinline__ int m() const { return (r.y >> 8) - (r.y & 0xff); }
 };
 
-// The records are fetched two groups ahead (load_records) and completed one group ahead (load_coeffs), so that
-// nothing in the loop waits for a load it has just issued.
-__device__ __forceinline__ void load_records(const TcArgs& A, int g, int q, Work& w) {
+// All three loads depend on the group number only, so a group's record can be fetched a whole group ahead.
+__device__ __forceinline__ void load_work(const TcArgs& A, int g, int q, int lane, Work& w) {
   w.h = __ldg(&A.groups[kRec * g]);
   w.r = __ldg(&A.groups[kRec * g + 2 + q]);
-}
-__device__ __forceinline__ void load_coeffs(const TcArgs& A, Work& w, int lane) {
-  w.cvec = 0.f;
-  if (w.valid()) {
-    const int K = min(w.l1(), w.m() + w.l2()) - max(-w.l1(), w.m() - w.l2()) + 1;
-    if (lane < K) w.cvec = __ldg(A.coeffs + w.r.w + lane);
-  }
+  w.t = __ldg(&A.groups[kRec * g + 1]);
+  w.cvec = lane < 16 ? __ldg(reinterpret_cast<const float*>(&A.groups[kRec * g + 6 + 4 * q]) + lane) : 0.f;
 }
 
 __device__ __noinline__ void fill_offsets(long long* dst, const PartView* parts, int nparts, const CellGrid& cg, long long cell) {
@@ -307,11 +313,13 @@ __device__ __noinline__ void flush_rows(const float* acc, const PartView* out, c
 
 __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_constant__ TcArgs A) {
   extern __shared__ __align__(128) unsigned char sm[];
-  uint64_t* aready = reinterpret_cast<uint64_t*>(sm);  // [2] A operand stored (4 worker warps arrive)
-  uint64_t* mdone_x = aready + 2;                      // [2] MMAs of the P product complete
-  uint64_t* mdone_y = aready + 4;                      // [2] MMAs of the Q product complete
-  uint32_t* tbase_s = reinterpret_cast<uint32_t*>(sm + 48);
-  long long* goff = reinterpret_cast<long long*>(sm + 64);
+  uint64_t* mdone_x = reinterpret_cast<uint64_t*>(sm);  // [2] MMAs of the P product complete (tcgen05.commit)
+  uint64_t* mdone_y = mdone_x + 2;                      // [2] MMAs of the Q product complete
+  // arrivals of the 8 warps of a set that have stored their part of an A operand; the last one issues the MMAs
+  int* evx = reinterpret_cast<int*>(sm + 32);           // [2]
+  int* evy = evx + 2;                                   // [2]
+  uint32_t* tbase_s = reinterpret_cast<uint32_t*>(sm + 96);
+  long long* goff = reinterpret_cast<long long*>(sm + 128);
   long long* xgoff = goff + kMaxParts;
   long long* ygoff = xgoff + kMaxParts;
   const float** gptr = reinterpret_cast<const float**>(ygoff + kMaxParts);  // g part base of this cell
@@ -330,9 +338,10 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_con
   }
   if (threadIdx.x == 32) {
     for (int s = 0; s < 2; s++) {
-      mbar_init(aready + s, 8);
       mbar_init(mdone_x + s, 1);
       mbar_init(mdone_y + s, 1);
+      evx[s] = 0;
+      evy[s] = 0;
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -357,11 +366,13 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_con
   tc_fence_after();
   const uint32_t tbase = *tbase_s;
 
-  if (warp < kWorkers) {
+  {
     // ------------------------------------------------ worker: half of one slab of every group of its set
     const int h = warp >> 3, s = (warp >> 2) & 1, q = warp & 3;
     const uint32_t lanes = (uint32_t)(32 * q) << 16;
-    const uint32_t tA = tbase + 256 * s + lanes, tDX = tA + 128, tDY = tA + 160;
+    // tensor-memory columns of set s: A operand (hi 64, lo 64) at 256 s, accumulators P and Q at + 128, + 160
+    const uint32_t tAX = tbase + 256 * s + lanes, tAY = tAX;
+    const uint32_t tDX = tAX + 128, tDY = tAX + 160;
     unsigned char* slot = ring + (4 * s + q) * kSlabBytes;
     const uint32_t slot_u32 = smem_u32(slot);
     const int pair_bar = 1 + 4 * s + q;  // named barrier of the two warps that share the slab
@@ -385,50 +396,61 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_con
       cp_async_commit();
     };
     auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory"); };
+    const uint32_t bt_u32 = smem_u32(bt);
+    Work cur{}, next{};  // the previous group's record is re-read (from L1) where its accumulators are added
+    // the MMAs of the current group's products, by whichever warp completed their preconditions
+    auto issue_x = [&]() {
+      tc_fence_after();
+      issue_product(tAX - lanes, tDX - lanes, bt_u32 + cur.t.x, cur.t.y);
+      mma_commit(mdone_x + s);
+    };
+    auto issue_y = [&]() {
+      tc_fence_after();
+      issue_product(tAY - lanes, tDY - lanes, bt_u32 + cur.t.z, cur.t.w);
+      mma_commit(mdone_y + s);
+    };
 
-    Work cur{}, prev{}, next{}, after{};  // `after`: records only
     if (ngs > 0) {
-      load_records(A, s, q, next);
-      load_coeffs(A, next, lane);
+      load_work(A, s, q, lane, next);
       prefetch(next);
-      if (ngs > 1) load_records(A, s + 2, q, after);
     }
     bool have_prev = false;
 
+    // Per group: store the P operand; (upper warps) add the previous Q result while the P MMAs run; store the Q
+    // operand when the P MMAs have released the block; (lower warps) add the P result while the Q MMAs run.
     // After a timeout (ok == false) the loop keeps its named barriers and arrivals but skips the work and the
     // waits, so that the two warps of a pair never wait for each other in vain.
     for (int k = 0; k < ngs; k++) {
       cur = next;
-      if (k + 1 < ngs) {
-        next = after;
-        load_coeffs(A, next, lane);
-      }
-      if (k + 2 < ngs) load_records(A, s + 2 * (k + 2), q, after);
+      if (k + 1 < ngs) load_work(A, s + 2 * (k + 1), q, lane, next);  // first used by the prefetch in step 3
 
       // 1. A operand of the P product: lane = row n1 of the slab, this warp's 32 of the 64 columns (n2, re/im)
       cp_async_wait_all();
       pair_sync();
-      if (cur.valid()) {
+      if (ok && cur.valid()) {
 #pragma unroll
-        for (int c4 = 0; c4 < 2; c4++) {
-          float v[16];
+        for (int c2 = 0; c2 < 4; c2++) {
+          float v[8];
 #pragma unroll
-          for (int i = 0; i < 4; i++) {
-            const int c = 8 * h + 4 * c4 + i;
+          for (int i = 0; i < 2; i++) {
+            const int c = 8 * h + 2 * c2 + i;
             const float4 f = *reinterpret_cast<const float4*>(slot + lane * 256 + ((c ^ (lane & 15)) << 4));
             v[4 * i] = f.x, v[4 * i + 1] = f.y, v[4 * i + 2] = f.z, v[4 * i + 3] = f.w;
           }
-          split_store16(tA, 32 * h + 16 * c4, v);
+          split_store8(tAX, 32 * h + 8 * c2, v);
         }
       }
       tmem_wait_st();
       tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(aready + s);
+      if (count_event(evx + s)) issue_x();
 
       // 2. the upper warps add the Q result of the previous group (overlaps this group's P MMAs)
-      if (ok && h == 1 && have_prev && prev.valid())
-        epilogue<false>(tDY, acc + prev.yacc(), prev.n2(), prev.b0() + lane, prev.m(), prev.l1(), prev.l2(), prev.cvec);
+      if (h == 1 && have_prev) {
+        Work prev;
+        load_work(A, s + 2 * (k - 1), q, lane, prev);
+        if (ok && prev.valid())
+          epilogue<false>(tDY, acc + prev.yacc(), prev.n2(), prev.b0() + lane, prev.m(), prev.l1(), prev.l2(), prev.cvec);
+      }
 
       // 3. A operand of the Q product, once the P MMAs have consumed the previous contents: the slab
       //    column-per-lane (lane = n2), this warp's 16 of the 32 rows n1 as columns (n1, re/im)
@@ -437,23 +459,22 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_con
       tc_fence_after();
       if (ok && cur.valid()) {
 #pragma unroll
-        for (int j = 0; j < 2; j++) {
-          float v[16];
+        for (int j = 0; j < 4; j++) {
+          float v[8];
 #pragma unroll
-          for (int i = 0; i < 8; i++) {
-            const int n1 = 16 * h + 8 * j + i;
+          for (int i = 0; i < 4; i++) {
+            const int n1 = 16 * h + 4 * j + i;
             const float2 f = *reinterpret_cast<const float2*>(slot + n1 * 256 + (((lane >> 1) ^ (n1 & 15)) << 4) + ((lane & 1) << 3));
             v[2 * i] = f.x, v[2 * i + 1] = f.y;
           }
-          split_store16(tA, 32 * h + 16 * j, v);
+          split_store8(tAY, 32 * h + 8 * j, v);
         }
       }
       pair_sync();  // both warps have read the slot: refill it with the next slab
       if (k + 1 < ngs) prefetch(next);
       tmem_wait_st();
       tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(aready + s);
+      if (count_event(evy + s)) issue_y();
 
       // 4. the lower warps add the P result (overlaps the Q MMAs)
       if (ok && h == 0 && cur.valid())
@@ -463,37 +484,11 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_con
       if (ok) ok = mbar_wait(mdone_y + s, par_y);
       par_y ^= 1;
       tc_fence_after();
-      prev = cur, have_prev = true;
+      have_prev = true;
     }
-    if (ok && h == 1 && have_prev && prev.valid())
-      epilogue<false>(tDY, acc + prev.yacc(), prev.n2(), prev.b0() + lane, prev.m(), prev.l1(), prev.l2(), prev.cvec);
+    if (ok && h == 1 && have_prev && cur.valid())
+      epilogue<false>(tDY, acc + cur.yacc(), cur.n2(), cur.b0() + lane, cur.m(), cur.l1(), cur.l2(), cur.cvec);
     cp_async_wait_all();
-    if (!ok && lane == 0) *A.status = 1;
-  } else {
-    // ------------------------------------------------ issuer of set s: 2 x 24 MMAs per group
-    const int s = warp - kWorkers;
-    const uint32_t tA = tbase + 256 * s, tDX = tA + 128, tDY = tA + 160;
-    const uint32_t bt_u32 = smem_u32(bt);
-    const int ngs = (A.ngroups - s + 1) >> 1;
-    uint32_t par_a = 0;
-    bool ok = true;
-    int4 hn = ngs > 0 ? __ldg(&A.groups[kRec * s + 1]) : make_int4(0, 0, 0, 0);
-    for (int k = 0; k < ngs && ok; k++) {
-      const int4 h = hn;  // {y table offset, y rows, x table offset, x rows}
-      if (k + 1 < ngs) hn = __ldg(&A.groups[kRec * (s + 2 * (k + 1)) + 1]);
-      ok = mbar_wait(aready + s, par_a);
-      par_a ^= 1;
-      if (!ok) break;
-      tc_fence_after();
-      issue_product(tA, tDX, bt_u32 + h.x, h.y);
-      mma_commit(mdone_x + s);
-      ok = mbar_wait(aready + s, par_a);
-      par_a ^= 1;
-      if (!ok) break;
-      tc_fence_after();
-      issue_product(tA, tDY, bt_u32 + h.z, h.w);
-      mma_commit(mdone_y + s);
-    }
     if (!ok && lane == 0) *A.status = 1;
   }
 
@@ -614,6 +609,19 @@ int launch_cg_bwd_tc(const VecCall& c, cudaStream_t s) {
                                       xs[xi].n | (ys[yi].n << 16), xacc[xi] | (yacc[yi] << 16)));
         p.h_items.push_back(make_int4(ybt[yi] + (b0 >> 5) * 512 * yR[yi], yR[yi], xbt[xi] + (a0 >> 5) * 512 * xR[xi], xR[xi]));
         for (int j = 0; j < 4; j++) p.h_items.push_back(j < ns ? v[i + j] : make_int4(0, 0, 0, 0));
+        for (int j = 0; j < 4; j++) {  // the band coefficients of the slab's row, zero-padded to 16
+          float c[16] = {0};
+          if (j < ns) {
+            const int l = v[i + j].y & 0xff, m = (v[i + j].y >> 8) - l;
+            const int K = std::min(xs[xi].l, m + ys[yi].l) - std::max(-xs[xi].l, m - ys[yi].l) + 1;
+            for (int e = 0; e < K; e++) c[e] = p.sched.coeffs[v[i + j].w + e];
+          }
+          for (int e = 0; e < 16; e += 4) {
+            int4 w;
+            memcpy(&w, c + e, 16);
+            p.h_items.push_back(w);
+          }
+        }
       }
     }
   });
