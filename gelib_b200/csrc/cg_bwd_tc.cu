@@ -123,6 +123,26 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+__device__ __forceinline__ float4 lds128(uint32_t a) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float2 lds64(uint32_t a) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ unsigned long long lds_u64(uint32_t a) {
+  unsigned long long v;
+  asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ unsigned long long cas_shared_u64(uint32_t a, unsigned long long expect, unsigned long long value) {
+  unsigned long long old;
+  asm volatile("atom.shared.cas.b64 %0, [%1], %2, %3;" : "=l"(old) : "r"(a), "l"(expect), "l"(value) : "memory");
+  return old;
+}
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -243,12 +263,15 @@ __device__ __forceinline__ void issue_product(uint32_t tA, uint32_t tD, uint32_t
 // latencies overlap; shared memory has no native float add, and an atomicAdd per float would serialise a
 // loop per entry.
 template <bool FOR_X>
-__device__ __forceinline__ void epilogue(uint32_t tD, float* accrows, int ntot, int ch, int m, int l1, int l2,
+__device__ __forceinline__ void epilogue(uint32_t tD, uint32_t accrows, int ntot, int ch, int m, int l1, int l2,
                                          float cvec) {
   const int lo = max(-l1, m - l2), hi = min(l1, m + l2);
   const int lb = FOR_X ? l2 : l1, lt = FOR_X ? l1 : l2;
   const int i0 = FOR_X ? (m - hi + lb) : (lo + lb), i1 = FOR_X ? (m - lo + lb) : (hi + lb);  // the band of idx
-  unsigned long long* base = reinterpret_cast<unsigned long long*>(accrows) + ch;
+  // entry idx: coefficient lane cl0 + cls * idx, target row (m + lb + lt) - idx
+  const int cl0 = FOR_X ? (m + lb - lo) : (-lb - lo), cls = FOR_X ? -1 : 1;
+  const uint32_t rowb = 8u * ntot;
+  const uint32_t chan = accrows + 8u * ch + (uint32_t)(m + lb + lt) * rowb;  // minus idx * rowb: the entry's address
   auto pack = [](float re, float im) { return ((unsigned long long)__float_as_uint(im) << 32) | __float_as_uint(re); };
   for (int j0 = i0; j0 <= i1; j0 += 4) {
     uint32_t dv[8];
@@ -260,29 +283,28 @@ __device__ __forceinline__ void epilogue(uint32_t tD, float* accrows, int ntot, 
     asm volatile("tcgen05.wait::ld.sync.aligned;"
                  : "+r"(dv[0]), "+r"(dv[1]), "+r"(dv[2]), "+r"(dv[3]), "+r"(dv[4]), "+r"(dv[5]), "+r"(dv[6]), "+r"(dv[7])::"memory");
     unsigned long long oldv[4], got[4];
-    unsigned long long* ptr[4];
+    uint32_t ptr[4];
     float2 add[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
       const int idx = min(j0 + i, i1);
-      const int mb = idx - lb, m1 = FOR_X ? m - mb : mb, mt = m - mb;
-      const float c = __shfl_sync(0xffffffffu, cvec, m1 - lo);
+      const float c = __shfl_sync(0xffffffffu, cvec, cl0 + cls * idx);
       add[i] = make_float2(c * __uint_as_float(dv[2 * i]), c * __uint_as_float(dv[2 * i + 1]));
-      ptr[i] = base + (mt + lt) * ntot;
-      oldv[i] = *ptr[i];
+      ptr[i] = chan - (uint32_t)idx * rowb;
+      oldv[i] = lds_u64(ptr[i]);
     }
 #pragma unroll
     for (int i = 0; i < 4; i++)
       if (j0 + i <= i1)
-        got[i] = atomicCAS(ptr[i], oldv[i],
-                           pack(__uint_as_float((uint32_t)oldv[i]) + add[i].x, __uint_as_float((uint32_t)(oldv[i] >> 32)) + add[i].y));
+        got[i] = cas_shared_u64(ptr[i], oldv[i],
+                                pack(__uint_as_float((uint32_t)oldv[i]) + add[i].x, __uint_as_float((uint32_t)(oldv[i] >> 32)) + add[i].y));
 #pragma unroll
     for (int i = 0; i < 4; i++)
       if (j0 + i <= i1)
         while (got[i] != oldv[i]) {  // another warp updated the entry in between: redo on its value
           oldv[i] = got[i];
-          got[i] = atomicCAS(ptr[i], oldv[i],
-                             pack(__uint_as_float((uint32_t)oldv[i]) + add[i].x, __uint_as_float((uint32_t)(oldv[i] >> 32)) + add[i].y));
+          got[i] = cas_shared_u64(ptr[i], oldv[i],
+                                  pack(__uint_as_float((uint32_t)oldv[i]) + add[i].x, __uint_as_float((uint32_t)(oldv[i] >> 32)) + add[i].y));
         }
   }
 }
@@ -396,7 +418,10 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_con
       cp_async_commit();
     };
     auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory"); };
-    const uint32_t bt_u32 = smem_u32(bt);
+    const uint32_t bt_u32 = smem_u32(bt), acc_u32 = smem_u32(acc);
+    // lane-constant parts of the swizzled slot addresses: row-per-lane reads and column-per-lane reads
+    const uint32_t xrd = slot_u32 + lane * 256, xsw = (lane & 15) << 4;
+    const uint32_t yrd = slot_u32 + ((lane & 1) << 3), ysw = (lane >> 1) << 4;
     Work cur{}, next{};  // the previous group's record is re-read (from L1) where its accumulators are added
     // the MMAs of the current group's products, by whichever warp completed their preconditions
     auto issue_x = [&]() {
@@ -434,7 +459,7 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_con
 #pragma unroll
           for (int i = 0; i < 2; i++) {
             const int c = 8 * h + 2 * c2 + i;
-            const float4 f = *reinterpret_cast<const float4*>(slot + lane * 256 + ((c ^ (lane & 15)) << 4));
+            const float4 f = lds128(xrd + ((c << 4) ^ xsw));
             v[4 * i] = f.x, v[4 * i + 1] = f.y, v[4 * i + 2] = f.z, v[4 * i + 3] = f.w;
           }
           split_store8(tAX, 32 * h + 8 * c2, v);
@@ -449,7 +474,7 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_con
         Work prev;
         load_work(A, s + 2 * (k - 1), q, lane, prev);
         if (ok && prev.valid())
-          epilogue<false>(tDY, acc + prev.yacc(), prev.n2(), prev.b0() + lane, prev.m(), prev.l1(), prev.l2(), prev.cvec);
+          epilogue<false>(tDY, acc_u32 + 4u * prev.yacc(), prev.n2(), prev.b0() + lane, prev.m(), prev.l1(), prev.l2(), prev.cvec);
       }
 
       // 3. A operand of the Q product, once the P MMAs have consumed the previous contents: the slab
@@ -464,7 +489,7 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_con
 #pragma unroll
           for (int i = 0; i < 4; i++) {
             const int n1 = 16 * h + 4 * j + i;
-            const float2 f = *reinterpret_cast<const float2*>(slot + n1 * 256 + (((lane >> 1) ^ (n1 & 15)) << 4) + ((lane & 1) << 3));
+            const float2 f = lds64(yrd + n1 * 256 + (((n1 & 15) << 4) ^ ysw));
             v[2 * i] = f.x, v[2 * i + 1] = f.y;
           }
           split_store8(tAY, 32 * h + 8 * j, v);
@@ -478,7 +503,7 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_con
 
       // 4. the lower warps add the P result (overlaps the Q MMAs)
       if (ok && h == 0 && cur.valid())
-        epilogue<true>(tDX, acc + cur.xacc(), cur.n1(), cur.a0() + lane, cur.m(), cur.l1(), cur.l2(), cur.cvec);
+        epilogue<true>(tDX, acc_u32 + 4u * cur.xacc(), cur.n1(), cur.a0() + lane, cur.m(), cur.l1(), cur.l2(), cur.cvec);
 
       // 5. the A block is free again when the Q MMAs are done
       if (ok) ok = mbar_wait(mdone_y + s, par_y);
@@ -487,7 +512,7 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_con
       have_prev = true;
     }
     if (ok && h == 1 && have_prev && cur.valid())
-      epilogue<false>(tDY, acc + cur.yacc(), cur.n2(), cur.b0() + lane, cur.m(), cur.l1(), cur.l2(), cur.cvec);
+      epilogue<false>(tDY, acc_u32 + 4u * cur.yacc(), cur.n2(), cur.b0() + lane, cur.m(), cur.l1(), cur.l2(), cur.cvec);
     cp_async_wait_all();
     if (!ok && lane == 0) *A.status = 1;
   }

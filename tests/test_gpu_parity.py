@@ -277,6 +277,60 @@ def test_vec_backward_is_reproducible_to_rounding(G):
         assert rel_err(a, b) < 2e-6
 
 
+# ---- the tensor-core (tcgen05) backward kernel: opt-in, for channel counts that are multiples of 32 ----------
+
+TC_CASES = [
+    (3, {l: 32 for l in range(4)}, {l: 32 for l in range(4)}, 3, TOL_BIG),
+    (2, {l: 32 for l in range(7)}, {l: 32 for l in range(7)}, 6, TOL_BIG),   # the headline channel layout
+    (2, {1: 64}, {2: 64}, -1, TOL_BIG),                                     # four 32 x 32 tiles per slab
+    (2, {0: 32, 1: 64}, {1: 32, 3: 96}, 4, TOL_BIG),                        # mixed channel counts
+    (1, {0: 32}, {0: 32}, 0, TOL_BIG),                                      # a single slab, three idle warps
+]
+
+
+@pytest.mark.parametrize("B,tau_x,tau_y,maxl,tol", TC_CASES)
+@pytest.mark.parametrize("bcast_y", [False, True])
+def test_vec_backward_tcgen05(G, oracle, monkeypatch, B, tau_x, tau_y, maxl, tol, bcast_y):
+    monkeypatch.setenv("GELIB_B200_BWD", "tcgen05!")  # fail instead of falling back to the SIMT kernel
+    x, y = _vec_inputs(tau_x, tau_y, B, 90)
+    if bcast_y:
+        y = {l: t[:1].contiguous() for l, t in y.items()}
+    tau_r = oracle.cg_type(tau_x, tau_y, maxl, False)
+    g = {l: crandn(400 + l, B, 2 * l + 1, n) for l, n in tau_r.items()}
+    gn = {l: np_c(t) for l, t in g.items()}
+    xg_w = {l: np.zeros(t.shape, np.complex64) for l, t in x.items()}
+    yg_w = {l: np.zeros(t.shape, np.complex64) for l, t in y.items()}
+    oracle.vec_cg_back0(xg_w, gn, {l: np_c(t) for l, t in y.items()}, False)
+    oracle.vec_cg_back1(yg_w, gn, {l: np_c(t) for l, t in x.items()}, False)
+    xv = G.backend.SO3vec.view([dev(t) for t in x.values()])
+    yv = G.backend.SO3vec.view([dev(t) for t in y.values()])
+    gv = G.backend.SO3vec.view([dev(t) for t in g.values()])
+    # accumulate on top of ones: the kernel adds to what is there
+    xg = [torch.ones(t.shape, dtype=torch.complex64, device="cuda") for t in x.values()]
+    yg = [torch.ones(t.shape, dtype=torch.complex64, device="cuda") for t in y.values()]
+    for _ in range(2):  # twice: the second call reuses the cached plan and the tensor memory
+        G.backend.SO3vec.addCGproduct_back01(G.backend.SO3vec.view(xg), G.backend.SO3vec.view(yg), gv, xv, yv)
+    torch.cuda.synchronize()
+    for p, w in zip(xg, xg_w.values()):
+        assert rel_err(p - 1, 2 * w) < tol
+    for p, w in zip(yg, yg_w.values()):
+        assert rel_err(p - 1, 2 * w) < tol
+
+
+def test_tcgen05_refuses_what_it_cannot_do(G, monkeypatch):
+    monkeypatch.setenv("GELIB_B200_BWD", "tcgen05!")
+    tau = {0: 8, 1: 8}
+    x, y = _vec_inputs(tau, tau, 2, 5)
+    xv = G.backend.SO3vec.view([dev(t) for t in x.values()])
+    yv = G.backend.SO3vec.view([dev(t) for t in y.values()])
+    tau_r = xv.get_tau().CGproduct(yv.get_tau(), 1).get_parts()
+    gv = G.backend.SO3vec.view([dev(crandn(7 + l, 2, 2 * l + 1, n)) for l, n in tau_r.items()])
+    xg = [torch.zeros(t.shape, dtype=torch.complex64, device="cuda") for t in x.values()]
+    yg = [torch.zeros(t.shape, dtype=torch.complex64, device="cuda") for t in y.values()]
+    with pytest.raises(Exception):
+        G.backend.SO3vec.addCGproduct_back01(G.backend.SO3vec.view(xg), G.backend.SO3vec.view(yg), gv, xv, yv)
+
+
 # ---- spherical harmonics --------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("L", [0, 1, 2, 4, 6, 8, 11, 14])
