@@ -230,9 +230,13 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--bwd-kernel", default="simt", choices=["simt", "tcgen05"],
                     help="backward kernel for channel counts that are multiples of 32: the default SIMT kernel or the tcgen05 one")
+    ap.add_argument("--fwd-kernel", default="simt", choices=["simt", "tcgen05"],
+                    help="forward kernel for channel counts that are multiples of 32")
     args = ap.parse_args()
     if args.bwd_kernel == "tcgen05":
         os.environ["GELIB_B200_BWD"] = "tcgen05"
+    if args.fwd_kernel == "tcgen05":
+        os.environ["GELIB_B200_FWD"] = "tcgen05"
     args.warmup = max(args.warmup, 0)
     desc, tx, ty, maxl, B, diag = WORKLOADS[args.workload]
     if args.batch:
@@ -365,7 +369,7 @@ def main():
                        "l2": "operands larger than L2 (output and upstream gradient %.1f GB each per GPU)"
                              % (work["fwd_bytes"] / 1e9),
                        "parallelism": "batch sharded over %d GPU(s), no collective on the data path" % world,
-                       "bwd_kernel": args.bwd_kernel},
+                       "fwd_kernel": args.fwd_kernel, "bwd_kernel": args.bwd_kernel},
             "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
             "cells_per_s": B * world / (tot_ms * 1e-3),
             "roofline": {"bound": "hbm", "kernel": "cg_%s_kernel" % ("fwd" if dom == "forward" else "bwd"),

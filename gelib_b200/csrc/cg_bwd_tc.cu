@@ -35,10 +35,13 @@
 #include <mutex>
 
 #include "plan.h"
+#include "tc_common.h"
 
 namespace gelib_b200 {
 
 namespace {
+
+using namespace tc;
 
 constexpr int kWorkers = 16;          // worker warps: two sets of four slabs, two warps per slab
 constexpr int kThreads = 32 * kWorkers;
@@ -46,8 +49,6 @@ constexpr int kSlots = 8;             // ring slots (one slab each)
 constexpr int kSlabBytes = 32 * 32 * 8;
 constexpr int kHeaderBytes = 896;     // mbarriers, tensor-memory base, cell offsets, g row pointers
 constexpr int kRec = 22;              // int4 per group record
-constexpr int kWaitLimit = 256;        // tries per wait, each parked for at most kSuspendNs
-constexpr uint32_t kSuspendNs = 1000000;
 
 struct TcArgs {
   PartView x[kMaxParts], y[kMaxParts], g[kMaxParts], xg[kMaxParts], yg[kMaxParts];
@@ -70,98 +71,10 @@ struct TcArgs {
   int* status;  // host-mapped: set to 1 when a wait timed out
 };
 
-// ---- PTX wrappers ----------------------------------------------------------------------------------------------
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-// Bounded wait for the phase with the given parity; false on timeout.  The suspend-time hint lets the hardware
-// park the warp until the phase completes instead of polling the shared-memory pipe that everybody else needs.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t a = smem_u32(bar);
-  for (int i = 0; i < kWaitLimit; i++) {
-    uint32_t ok;
-    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
-                 : "=r"(ok)
-                 : "r"(a), "r"(parity), "r"(kSuspendNs)
-                 : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
-// Counts one arrival; true in every lane of the warp that arrives eighth.
-__device__ __forceinline__ bool count_event(int* counter) {
-  int old = 0;
-  __syncwarp();
-  if ((threadIdx.x & 31) == 0) {
-    __threadfence_block();
-    old = atomicAdd(counter, 1);
-    __threadfence_block();
-  }
-  old = __shfl_sync(0xffffffffu, old, 0);
-  return (old & 7) == 7;
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// D[tmem] (+)= A[tmem] * B[smem descriptor]; issued by one elected lane of a converged warp.
-__device__ __forceinline__ void mma_tf32_ts(uint32_t d, uint32_t a, uint64_t bdesc, uint32_t idesc, bool accumulate) {
-  asm volatile(
-      "{ .reg .pred P, Q; elect.sync _|P, 0xffffffff; setp.ne.b32 Q, %4, 0;\n"
-      "@P tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, Q; }" ::"r"(d), "r"(a), "l"(bdesc), "r"(idesc),
-      "r"((uint32_t)accumulate)
-      : "memory");
-}
-// Arrives on the mbarrier when all MMAs issued so far by this thread have completed.
-__device__ __forceinline__ void mma_commit(uint64_t* bar) {
-  asm volatile(
-      "{ .reg .pred P; elect.sync _|P, 0xffffffff;\n"
-      "@P tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0]; }" ::"r"(smem_u32(bar))
-      : "memory");
-}
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ float4 lds128(uint32_t a) {
-  float4 v;
-  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ float2 lds64(uint32_t a) {
-  float2 v;
-  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ unsigned long long lds_u64(uint32_t a) {
-  unsigned long long v;
-  asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ unsigned long long cas_shared_u64(uint32_t a, unsigned long long expect, unsigned long long value) {
-  unsigned long long old;
-  asm volatile("atom.shared.cas.b64 %0, [%1], %2, %3;" : "=l"(old) : "r"(a), "l"(expect), "l"(value) : "memory");
-  return old;
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-
-__device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) {
-  hi = __float_as_uint(v) & 0xffffe000u;
-  lo = __float_as_uint(v - __uint_as_float(hi));
-}
-
-__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
-               "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-               : "memory");
-}
+// ---- PTX wrappers: tc_common.h ------------------------------------------------------------------------------
 
 // Splits 8 values and stores them to columns [col, col+8) of the hi block and of the lo block (64 columns on).
-// Eight at a time keeps the live registers low: the kernel runs 18 warps at 96 registers per thread.
+// Eight at a time keeps the live registers low.
 __device__ __forceinline__ void split_store8(uint32_t tA, int col, const float (&v)[8]) {
   uint32_t hi[8], lo[8];
 #pragma unroll
@@ -467,7 +380,7 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_con
       }
       tmem_wait_st();
       tc_fence_before();
-      if (count_event(evx + s)) issue_x();
+      if (count_event(evx + s, 7)) issue_x();
 
       // 2. the upper warps add the Q result of the previous group (overlaps this group's P MMAs)
       if (h == 1 && have_prev) {
@@ -499,7 +412,7 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_con
       if (k + 1 < ngs) prefetch(next);
       tmem_wait_st();
       tc_fence_before();
-      if (count_event(evy + s)) issue_y();
+      if (count_event(evy + s, 7)) issue_y();
 
       // 4. the lower warps add the P result (overlaps the Q MMAs)
       if (ok && h == 0 && cur.valid())

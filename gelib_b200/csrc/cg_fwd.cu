@@ -17,6 +17,8 @@
 // No thread ever needs another thread's partial result: there are no shuffles, atomics or barriers
 // after the staging barrier.
 #include <algorithm>
+#include <cstdlib>
+#include <string>
 
 #include "plan.h"
 
@@ -216,6 +218,14 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 int launch_cg_fwd(const VecCall& c, cudaStream_t s) {
   static const char* fn = "SO3vec_addCGproduct";
+  // GELIB_B200_FWD=tcgen05 sends calls that qualify (channel counts that are multiples of 32, output overwritten)
+  // to the tensor-core kernel of cg_fwd_tc.cu; "tcgen05!" refuses calls that do not qualify instead of falling back.
+  const char* which = getenv("GELIB_B200_FWD");
+  if (which && (std::string(which) == "tcgen05" || std::string(which) == "tcgen05!")) {
+    const int rc = launch_cg_fwd_tc(c, s);
+    if (rc != -1) return rc;
+    if (std::string(which) == "tcgen05!") return fail(GELIB_INVALID, fn, "the call does not qualify for the tcgen05 kernel");
+  }
   // ---- choose the lane layout: least padded work on the dominant channel counts, then the widest tile
   int n1 = 1, n2 = 1;
   for (const auto& p : c.x) n1 = std::max(n1, p.n);

@@ -317,6 +317,25 @@ def test_vec_backward_tcgen05(G, oracle, monkeypatch, B, tau_x, tau_y, maxl, tol
         assert rel_err(p - 1, 2 * w) < tol
 
 
+@pytest.mark.parametrize("B,tau_x,tau_y,maxl,tol", TC_CASES)
+def test_vec_forward_tcgen05(G, oracle, monkeypatch, B, tau_x, tau_y, maxl, tol):
+    monkeypatch.setenv("GELIB_B200_FWD", "tcgen05!")  # fail instead of falling back to the SIMT kernel
+    x, y = _vec_inputs(tau_x, tau_y, B, 60)
+    tau_r = oracle.cg_type(tau_x, tau_y, maxl, False)
+    want = {l: np.zeros((B, 2 * l + 1, n), np.complex64) for l, n in tau_r.items()}
+    oracle.vec_cg(want, {l: np_c(t) for l, t in x.items()}, {l: np_c(t) for l, t in y.items()}, False)
+    xv = G.backend.SO3vec.view([dev(t) for t in x.values()])
+    yv = G.backend.SO3vec.view([dev(t) for t in y.values()])
+    # the output starts as garbage: the kernel overwrites every element
+    rparts = [torch.full((B, 2 * l + 1, n), 7.0 + 3.0j, dtype=torch.complex64, device="cuda") for l, n in tau_r.items()]
+    rv = G.backend.SO3vec.view(rparts)
+    for _ in range(2):  # twice: the second call reuses the cached plan and the tensor memory
+        rv.addCGproduct(xv, yv, overwrite=True)
+    torch.cuda.synchronize()
+    for p, (l, w) in zip(rparts, want.items()):
+        assert rel_err(p, w) < TOL, l
+
+
 def test_tcgen05_refuses_what_it_cannot_do(G, monkeypatch):
     monkeypatch.setenv("GELIB_B200_BWD", "tcgen05!")
     tau = {0: 8, 1: 8}
