@@ -230,13 +230,12 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--bwd-kernel", default="simt", choices=["simt", "tcgen05"],
                     help="backward kernel for channel counts that are multiples of 32: the default SIMT kernel or the tcgen05 one")
-    ap.add_argument("--fwd-kernel", default="simt", choices=["simt", "tcgen05"],
+    ap.add_argument("--fwd-kernel", default="auto", choices=["auto", "simt", "tcgen05"],
                     help="forward kernel for channel counts that are multiples of 32")
     args = ap.parse_args()
     if args.bwd_kernel == "tcgen05":
         os.environ["GELIB_B200_BWD"] = "tcgen05"
-    if args.fwd_kernel == "tcgen05":
-        os.environ["GELIB_B200_FWD"] = "tcgen05"
+    os.environ["GELIB_B200_FWD"] = args.fwd_kernel
     args.warmup = max(args.warmup, 0)
     desc, tx, ty, maxl, B, diag = WORKLOADS[args.workload]
     if args.batch:

@@ -311,8 +311,9 @@ inline int round_up(int v, int q) { return (v + q - 1) / q * q; }
 
 }  // namespace
 
-// Returns -1 when the call does not qualify (the caller then takes the SIMT kernel).
-int launch_cg_fwd_tc(const VecCall& c, cudaStream_t s) {
+// Returns -1 when the call does not qualify or has fewer than min_slabs slabs per cell (the caller then takes the
+// SIMT kernel).
+int launch_cg_fwd_tc(const VecCall& c, cudaStream_t s, int min_slabs) {
   static const char* fn = "SO3vec_addCGproduct";
   if (!c.vec_ok || !(c.flags & GELIB_OVERWRITE) || c.r_bcast) return -1;
   if (c.x.size() > 15 || c.y.size() > 15 || c.r.size() > 15) return -1;
@@ -401,6 +402,7 @@ int launch_cg_fwd_tc(const VecCall& c, cudaStream_t s) {
     }
   });
   if (!plan) return GELIB_CUDA_ERROR;
+  if (4 * (plan->nitems / kRec) < min_slabs) return -1;  // groups of four slabs (the last one of a table may be partial)
   if (plan->nitems == 0 || c.cg.ncells == 0) return GELIB_OK;
   if (c.cg.ncells > 0x7fffffffLL) return fail(GELIB_SKIPPED, fn, "number of cells exceeds 2^31-1");
 

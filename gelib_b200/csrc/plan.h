@@ -29,7 +29,7 @@ DevicePlan* get_plan(const std::vector<int>& key, const std::function<void(Devic
 
 // Kernel families (each returns a status code).
 int launch_cg_fwd(const VecCall& c, cudaStream_t s);
-int launch_cg_fwd_tc(const VecCall& c, cudaStream_t s);  // tcgen05 kernel; -1 when the call does not qualify
+int launch_cg_fwd_tc(const VecCall& c, cudaStream_t s, int min_slabs);  // tcgen05 kernel; -1 when the call does not qualify or has fewer slabs per cell
 int launch_cg_bwd(const VecCall& c, cudaStream_t s);
 int launch_cg_bwd_tc(const VecCall& c, cudaStream_t s);  // tcgen05 kernel; -1 when the call does not qualify
 int launch_cg_narrow_bwd(const VecCall& c, cudaStream_t s);
