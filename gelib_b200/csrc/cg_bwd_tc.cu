@@ -473,12 +473,7 @@ int launch_cg_bwd_tc(const VecCall& c, cudaStream_t s) {
   for (const auto& p : c.x) if (p.n % 32 || p.l > 7 || p.n > 32768) return -1;
   for (const auto& p : c.y) if (p.n % 32 || p.l > 7 || p.n > 32768) return -1;
   for (const auto& p : c.r) if (p.l > 127) return -1;
-  int dev = 0, cc_major = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
-    cudaGetLastError();
-    return -1;
-  }
-  if (cc_major != 10) return -1;
+  if (!device_has_tcgen05()) return -1;
   int* status = status_word();
   if (!status) return -1;
   if (*status != 0) {

@@ -21,6 +21,7 @@
 // loop, frees its tensor memory and returns, and the next call reports the failure.
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -320,12 +321,15 @@ int launch_cg_fwd_tc(const VecCall& c, cudaStream_t s, int min_slabs) {
   for (const auto& p : c.x) if (p.n % 32 || p.l > 7 || p.n > 32768) return -1;
   for (const auto& p : c.y) if (p.n % 32 || p.l > 7 || p.n > 32768) return -1;
   for (const auto& p : c.r) if (p.l > 127) return -1;
-  int dev = 0, cc_major = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
-    cudaGetLastError();
-    return -1;
+  if (min_slabs > 0) {  // cheap count of the slabs per cell before any set-up: small calls leave here
+    long long slabs = 0;
+    for (const auto& px : c.x)
+      for (const auto& py : c.y)
+        for (const auto& pr : c.r)
+          if (pr.l >= std::abs(px.l - py.l) && pr.l <= px.l + py.l) slabs += (long long)(2 * pr.l + 1) * (px.n / 32) * (py.n / 32);
+    if (slabs < min_slabs) return -1;
   }
-  if (cc_major != 10) return -1;
+  if (!device_has_tcgen05()) return -1;
   int* status = fwd_status_word();
   if (!status) return -1;
   if (*status != 0) {
@@ -402,7 +406,6 @@ int launch_cg_fwd_tc(const VecCall& c, cudaStream_t s, int min_slabs) {
     }
   });
   if (!plan) return GELIB_CUDA_ERROR;
-  if (4 * (plan->nitems / kRec) < min_slabs) return -1;  // groups of four slabs (the last one of a table may be partial)
   if (plan->nitems == 0 || c.cg.ncells == 0) return GELIB_OK;
   if (c.cg.ncells > 0x7fffffffLL) return fail(GELIB_SKIPPED, fn, "number of cells exceeds 2^31-1");
 

@@ -30,6 +30,26 @@ bool upload(const std::vector<T>& h, T** d) {
 }
 }  // namespace
 
+bool device_has_tcgen05() {
+  static std::mutex mu;
+  static int cc_major[64];  // 0 = not asked yet, -1 = query failed
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return false;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (cc_major[dev] == 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+      cudaGetLastError();
+      v = -1;
+    }
+    cc_major[dev] = v;
+  }
+  return cc_major[dev] == 10;
+}
+
 DevicePlan* get_plan(const std::vector<int>& key, const std::function<void(DevicePlan&)>& build) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) {

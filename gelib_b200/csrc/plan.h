@@ -44,6 +44,7 @@ void build_diag_items(DevicePlan& p, const std::vector<PartSig>& xs, const std::
                       const std::vector<PartSig>& rs, int* max_nl);
 int launch_spharm(const std::vector<PartView>& r, const PartView& x, const CellGrid& cg, int flags, cudaStream_t s);
 
+bool device_has_tcgen05();  // compute capability 10.x on the current device (cached per device)
 long long launch_count();
 const std::string& last_error();
 
