@@ -77,6 +77,18 @@ def algorithmic_work(tx, ty, maxl, B, diag):
 TRAFFIC_RATIO = {("cfg3", "forward"): 0.98, ("cfg3", "backward"): 1.002}
 
 
+def kernel_name(args, dom):
+    """Name of the kernel the roofline object describes (the slower of the step's two kernels)."""
+    if args.workload == "cfg4":
+        return "diag_fwd_cell_kernel" if dom == "forward" else "diag_bwd_cell_kernel"
+    if args.workload == "cfg5":
+        return "cg_narrow_fwd_kernel" if dom == "forward" else "cg_narrow_bwd_kernel"
+    if dom == "forward":
+        tc = args.fwd_kernel == "tcgen05" or (args.fwd_kernel == "auto" and args.workload == "cfg3")
+        return "cg_fwd_tc_kernel" if tc else "cg_fwd_kernel"
+    return "cg_bwd_tc_kernel" if args.bwd_kernel == "tcgen05" else "cg_bwd_kernel"
+
+
 def measured_peak():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -371,7 +383,7 @@ def main():
                        "fwd_kernel": args.fwd_kernel, "bwd_kernel": args.bwd_kernel},
             "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
             "cells_per_s": B * world / (tot_ms * 1e-3),
-            "roofline": {"bound": "hbm", "kernel": "cg_%s_kernel" % ("fwd" if dom == "forward" else "bwd"),
+            "roofline": {"bound": "hbm", "kernel": kernel_name(args, dom),
                          "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": peak_kind,
                          "traffic": (TRAFFIC_RATIO[(args.workload, dom)] * (work["fwd_bytes"] if dom == "forward" else work["bwd_bytes"])
                                      if (args.workload, dom) in TRAFFIC_RATIO else None),
