@@ -337,12 +337,40 @@ def main():
         h2d = sum(t.numel() * 8 for t in hx)
         d2h = sum(t.numel() * 8 for t in hg)
 
+        # The step in NC batch chunks through the public API (batch slices are plain views): the copies of a chunk
+        # run on their own streams beside the kernels of its neighbours, as a caller with host data would do it.
+        NC = 4 if B >= 64 else 1
+        bounds = [(B * c // NC, B * (c + 1) // NC) for c in range(NC)]
+        s_in, s_out, s_main = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+        chunks = []
+        for c0, c1 in bounds:
+            sl = lambda ts: [t[c0:c1] for t in ts]
+            chunks.append({
+                "x": gb.SO3vec.view(sl(xs)), "y": gb.SO3vec.view(sl(ys)), "r": gb.SO3vec.view(sl(rs)), "g": gb.SO3vec.view(sl(gs)),
+                "xg": gb.SO3vec.view(sl(xg)), "yg": gb.SO3vec.view(sl(yg)),
+                "dev_in": sl(xs + ys), "host_in": sl(hx), "dev_out": sl(xg + yg), "host_out": sl(hg),
+                "ev_in": torch.cuda.Event(), "ev_done": torch.cuda.Event()})
+
         def e2e_step():
-            for d, h in zip(xs + ys, hx):
-                d.copy_(h, non_blocking=True)
-            step()
-            for h, d in zip(hg, xg + yg):
-                h.copy_(d, non_blocking=True)
+            s_in.wait_stream(s_main)    # the previous step's kernels no longer read x, y
+            s_out.wait_stream(s_main)
+            for ch in chunks:
+                with torch.cuda.stream(s_in):
+                    for d, h in zip(ch["dev_in"], ch["host_in"]):
+                        d.copy_(h, non_blocking=True)
+                    ch["ev_in"].record(s_in)
+                s_main.wait_event(ch["ev_in"])
+                (ch["r"].addDiagCGproduct if diag else ch["r"].addCGproduct)(ch["x"], ch["y"], overwrite=True)
+                for t in ch["dev_out"]:
+                    t.zero_()
+                bwd(ch["xg"], ch["yg"], ch["g"], ch["x"], ch["y"])
+                ch["ev_done"].record(s_main)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ch["ev_done"])
+                    for h, d in zip(ch["host_out"], ch["dev_out"]):
+                        h.copy_(d, non_blocking=True)
+            s_main.wait_stream(s_out)   # the step ends when its gradients are on the host
+            s_main.wait_stream(s_in)
 
         e2e_step()
         sync_all()
