@@ -16,6 +16,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("{ .reg .b64 t; mbarrier.arrive.shared::cta.b64 t, [%0]; }" ::"r"(smem_u32(bar)) : "memory");
+}
 // Bounded wait for the phase with the given parity; false on timeout.  The suspend-time hint lets the hardware
 // park the warp until the phase completes instead of polling the shared-memory pipe that everybody else needs.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
