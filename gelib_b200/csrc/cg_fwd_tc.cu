@@ -59,6 +59,7 @@ struct FwdTcArgs {
   int ngroups;
   int offs_extra;
   int* status;
+  int drop_commit;  // test hook: the MMAs are issued but never committed, so every wait of the kernel runs out
 };
 
 struct Slab {
@@ -248,7 +249,7 @@ __global__ void __launch_bounds__(kThreads, 1) cg_fwd_tc_kernel(const __grid_con
 #pragma unroll 1
           for (int ks = 0; ks < ksteps; ks++) mma_tf32_ts(tDs, a + 8 * ks, b + 128ull * ks, idesc, (term | ks) != 0);
         }
-        mma_commit(mdone + s);
+        if (!A.drop_commit) mma_commit(mdone + s);
       }
 
       // 2. the accumulator rows of the slab: 256 contiguous bytes of the output per lane
@@ -413,6 +414,9 @@ int launch_cg_fwd_tc(const VecCall& c, cudaStream_t s, int min_slabs) {
   a.groups = plan->items;
   a.ngroups = plan->nitems / kRec;
   a.offs_extra = c.offs_extra;
+  // GELIB_B200_INJECT_TIMEOUT=1 (tests only): exercise the bounded waits and the status word without any fault
+  const char* inject = getenv("GELIB_B200_INJECT_TIMEOUT");
+  a.drop_commit = inject && atoi(inject) != 0;
   a.status = status;  // unified addressing: the host pointer of mapped memory is valid on the device
   cudaError_t e = cudaFuncSetAttribute(cg_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e == cudaSuccess) {

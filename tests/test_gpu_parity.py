@@ -336,6 +336,32 @@ def test_vec_forward_tcgen05(G, oracle, monkeypatch, B, tau_x, tau_y, maxl, tol)
         assert rel_err(p, w) < TOL, l
 
 
+def test_tcgen05_wait_that_runs_out_is_reported(G, oracle, monkeypatch):
+    """The kernel's mbarrier waits are bounded: when the completion never arrives (injected on the host: the MMAs
+    are issued but not committed) the kernel gives up within a fraction of a second, frees its tensor memory and
+    returns; the next call reports it, and the one after that works again."""
+    monkeypatch.setenv("GELIB_B200_FWD", "tcgen05!")
+    tau = {l: 32 for l in range(3)}
+    x, y = _vec_inputs(tau, tau, 2, 77)
+    tau_r = oracle.cg_type(tau, tau, 2, False)
+    xv = G.backend.SO3vec.view([dev(t) for t in x.values()])
+    yv = G.backend.SO3vec.view([dev(t) for t in y.values()])
+    rparts = [torch.zeros(2, 2 * l + 1, n, dtype=torch.complex64, device="cuda") for l, n in tau_r.items()]
+    rv = G.backend.SO3vec.view(rparts)
+    monkeypatch.setenv("GELIB_B200_INJECT_TIMEOUT", "1")
+    rv.addCGproduct(xv, yv, overwrite=True)   # launches; its waits run out on the device
+    torch.cuda.synchronize()                  # the context stays usable
+    monkeypatch.delenv("GELIB_B200_INJECT_TIMEOUT")
+    with pytest.raises(Exception, match="gave up waiting"):
+        rv.addCGproduct(xv, yv, overwrite=True)
+    rv.addCGproduct(xv, yv, overwrite=True)   # the status was cleared: this one computes
+    torch.cuda.synchronize()
+    want = {l: np.zeros((2, 2 * l + 1, n), np.complex64) for l, n in tau_r.items()}
+    oracle.vec_cg(want, {l: np_c(t) for l, t in x.items()}, {l: np_c(t) for l, t in y.items()}, False)
+    for p, (l, w) in zip(rparts, want.items()):
+        assert rel_err(p, w) < TOL, l
+
+
 def test_tcgen05_refuses_what_it_cannot_do(G, monkeypatch):
     monkeypatch.setenv("GELIB_B200_BWD", "tcgen05!")
     tau = {0: 8, 1: 8}
