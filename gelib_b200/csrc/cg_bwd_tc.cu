@@ -15,16 +15,20 @@
 // The MMAs run as tcgen05.mma kind::tf32 with the 3xTF32 split (a = a_hi + a_lo with a_hi the upper 19 bits;
 // a_lo b_hi + a_hi b_lo + a_hi b_hi, FP32 accumulation in tensor memory), which keeps FP32-level accuracy.
 //
-// Data movement per CTA (one cell).  At start the x and y rows are written to shared memory once, already split
-// and in the K-major core-matrix layout the B operand descriptor wants (rows 2*mi and 2*mi+1 = the two parts).
-// Eight worker warps each own one slab at a time: cp.async brings it into the warp's 8 KB ring slot
-// (16-byte chunks XOR-swizzled by row), the warp reads it row-per-lane, splits it and stores it to tensor memory
-// as the A operand of the P product (lane = n1, columns = (n2,c)), later column-per-lane for the Q product
-// (lane = n2, columns = (n1,c)); A never passes through shared memory again.  Warps 0-3 and 4-7 form two sets
-// with their own tensor-memory columns (A 128, P 32, Q 32) and their own issuing warp (8, 9), so that one set's
-// MMAs overlap the other's loads, splits and epilogues.  The epilogue reads the accumulator row of its lane with
-// tcgen05.ld and adds into gradient rows in shared memory with shared-memory atomics; the rows go to global
-// memory once at the end.  Gradients are reproducible to rounding, not bitwise.
+// Data movement.  One CTA per (cell, product): the P CTA holds the y tables and the x gradient rows, the Q CTA the x
+// tables and the y gradient rows; the two CTAs of a cell start next to each other, so the second read of a slab
+// normally comes from L2.  At start the CTA writes its tables to shared memory once, already split and in the
+// K-major core-matrix layout the B operand descriptor wants (rows 2*mi and 2*mi+1 = the two parts).  Sixteen warps
+// each own one slab at a time: cp.async brings it into the warp's 8 KB ring slot (16-byte chunks XOR-swizzled by
+// row); the warp reads it row-per-lane (P: lane = n1, columns (n2,c)) or column-per-lane (Q: lane = n2, columns
+// (n1,c)), splits it and stores it to tensor memory as the A operand, one K half (32 of the 64 columns) at a time;
+// A never passes through shared memory again.  Four sets of four warps own 128 tensor-memory columns each (A hi 32,
+// A lo 32, two accumulators of 32): the warp whose store completes an operand half (a shared-memory arrival counter)
+// issues its 12 MMAs and a tcgen05.commit; the second half is read and the ring slot refilled while the first
+// half's MMAs run, and the previous group's accumulator is added to the gradient rows while the second half's run.
+// The epilogue reads the accumulator row of its lane with tcgen05.ld at the columns of the band and adds into
+// gradient rows in shared memory with batched 64-bit compare-and-swap; the rows go to global memory once at the
+// end.  Gradients are reproducible to rounding, not bitwise.
 //
 // Every wait on an mbarrier is bounded; on a timeout the kernel records it in a host-mapped status word,
 // leaves its loops, frees its tensor memory and returns, and the next call reports the failure.
@@ -43,9 +47,9 @@ namespace {
 
 using namespace tc;
 
-constexpr int kWorkers = 16;          // worker warps: two sets of four slabs, two warps per slab
+constexpr int kWorkers = 16;          // four sets of four slabs, one warp per slab
 constexpr int kThreads = 32 * kWorkers;
-constexpr int kSlots = 8;             // ring slots (one slab each)
+constexpr int kSlots = 16;            // ring slots (one slab each, one per warp)
 constexpr int kSlabBytes = 32 * 32 * 8;
 constexpr int kHeaderBytes = 896;     // mbarriers, tensor-memory base, cell offsets, g row pointers
 constexpr int kRec = 22;              // int4 per group record
@@ -73,14 +77,14 @@ struct TcArgs {
 
 // ---- PTX wrappers: tc_common.h ------------------------------------------------------------------------------
 
-// Splits 8 values and stores them to columns [col, col+8) of the hi block and of the lo block (64 columns on).
+// Splits 8 values and stores them to columns [col, col+8) of the hi block and of the lo block (32 columns on).
 // Eight at a time keeps the live registers low.
 __device__ __forceinline__ void split_store8(uint32_t tA, int col, const float (&v)[8]) {
   uint32_t hi[8], lo[8];
 #pragma unroll
   for (int i = 0; i < 8; i++) split_tf32(v[i], hi[i], lo[i]);
   tmem_st8(tA + col, hi);
-  tmem_st8(tA + 64 + col, lo);
+  tmem_st8(tA + 32 + col, lo);
 }
 
 // ---- kernel pieces ---------------------------------------------------------------------------------------------
@@ -147,23 +151,25 @@ __device__ __noinline__ void stage_tables(unsigned char* bt, const PartView* par
   }
 }
 
-// The 24 MMAs of one product of a group: D[128 x N] = A_lo B_hi + A_hi B_lo + A_hi B_hi over K = 64 in steps of 8.
-// tA: tensor-memory column of the set's A block (hi at +0, lo at +64); table: shared address of the B table.
-__device__ __forceinline__ void issue_product(uint32_t tA, uint32_t tD, uint32_t table, int R) {
+// The 12 MMAs of one K half of a group's product: D[128 x N] (+)= A_lo B_hi + A_hi B_lo + A_hi B_hi over 32 of the
+// K = 64 in steps of 8.  tA: tensor-memory column of the set's A block (hi at +0, lo at +32); table: shared address
+// of the B table; half: which 32 K values; init: overwrite the accumulator (first half) or add to it.
+__device__ __forceinline__ void issue_half(uint32_t tA, uint32_t tD, uint32_t table, int R, int half, bool init) {
   const uint32_t N = R <= 16 ? 16u : 32u;
   // instruction descriptor: D = F32, A = B = TF32, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
   const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((N >> 3) << 17) | ((128u >> 4) << 24);
   // shared-memory descriptor, no swizzle, K-major: start >> 4, leading (k-chunk) offset R*16 B, stride (8-row
-  // group) offset 128 B, descriptor version 1
+  // group) offset 128 B, descriptor version 1; a half is 8 k-chunks = 128 R bytes on
   const uint64_t fixed = ((uint64_t)R << 16) | (8ull << 32) | (1ull << 46);
-  const uint64_t dhi = fixed | ((table >> 4) & 0x3fffu), dlo = fixed | (((table + 256u * R) >> 4) & 0x3fffu);
+  const uint32_t t0 = table + 128u * R * half;
+  const uint64_t dhi = fixed | ((t0 >> 4) & 0x3fffu), dlo = fixed | (((t0 + 256u * R) >> 4) & 0x3fffu);
   const uint64_t kstep = 2ull * R;  // two k-chunks per MMA, in 16-byte units
 #pragma unroll
   for (int term = 0; term < 3; term++) {
-    const uint32_t a = term == 0 ? tA + 64 : tA;  // a_lo b_hi, a_hi b_lo, a_hi b_hi: smallest terms first
+    const uint32_t a = term == 0 ? tA + 32 : tA;  // a_lo b_hi, a_hi b_lo, a_hi b_hi: smallest terms first
     const uint64_t b = term == 1 ? dlo : dhi;
 #pragma unroll
-    for (int ks = 0; ks < 8; ks++) mma_tf32_ts(tD, a + 8 * ks, b + ks * kstep, idesc, (term | ks) != 0);
+    for (int ks = 0; ks < 4; ks++) mma_tf32_ts(tD, a + 8 * ks, b + ks * kstep, idesc, !init || (term | ks) != 0);
   }
 }
 
@@ -248,23 +254,22 @@ __device__ __noinline__ void flush_rows(const float* acc, const PartView* out, c
 
 __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_constant__ TcArgs A) {
   extern __shared__ __align__(128) unsigned char sm[];
-  uint64_t* mdone_x = reinterpret_cast<uint64_t*>(sm);  // [2] MMAs of the P product complete (tcgen05.commit)
-  uint64_t* mdone_y = mdone_x + 2;                      // [2] MMAs of the Q product complete
-  // arrivals of the 8 warps of a set that have stored their part of an A operand; the last one issues the MMAs
-  int* evx = reinterpret_cast<int*>(sm + 32);           // [2]
-  int* evy = evx + 2;                                   // [2]
+  uint64_t* mdone = reinterpret_cast<uint64_t*>(sm);  // [4] MMAs of a set's current K half complete (tcgen05.commit)
+  int* ev = reinterpret_cast<int*>(sm + 32);          // [4] arrivals of the set's warps that have stored their A rows
   uint32_t* tbase_s = reinterpret_cast<uint32_t*>(sm + 96);
   long long* goff = reinterpret_cast<long long*>(sm + 128);
-  long long* xgoff = goff + kMaxParts;
-  long long* ygoff = xgoff + kMaxParts;
-  const float** gptr = reinterpret_cast<const float**>(ygoff + kMaxParts);  // g part base of this cell
+  long long* ogoff = goff + kMaxParts;                                      // offsets of the CTA's output vector
+  const float** gptr = reinterpret_cast<const float**>(ogoff + kMaxParts);  // g part base of this cell
   long long* gsm = reinterpret_cast<long long*>(gptr + kMaxParts);          // g row stride
   unsigned char* bt = sm + kHeaderBytes;
   float* acc = reinterpret_cast<float*>(bt + A.bt_bytes);
   unsigned char* ring = reinterpret_cast<unsigned char*>(acc + A.acc_floats);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long cell = blockIdx.x;
+  // one CTA per (cell, product): product 0 = P (gradient of x, needs the y tables), 1 = Q (gradient of y, x tables);
+  // the two CTAs of a cell start next to each other, so the second read of a slab normally comes from L2
+  const int product = blockIdx.x & 1;
+  const long long cell = blockIdx.x >> 1;
 
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tbase_s)), "r"(512u)
@@ -272,17 +277,17 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_con
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (threadIdx.x == 32) {
-    for (int s = 0; s < 2; s++) {
-      mbar_init(mdone_x + s, 1);
-      mbar_init(mdone_y + s, 1);
-      evx[s] = 0;
-      evy[s] = 0;
+    for (int s = 0; s < 4; s++) {
+      mbar_init(mdone + s, 1);
+      ev[s] = 0;
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   fill_offsets(goff, A.g, A.ng, A.cg, cell);
-  fill_offsets(xgoff, A.xg, A.nx, A.cg, cell);
-  fill_offsets(ygoff, A.yg, A.ny, A.cg, cell);
+  if (product == 0)
+    fill_offsets(ogoff, A.xg, A.nx, A.cg, cell);
+  else
+    fill_offsets(ogoff, A.yg, A.ny, A.cg, cell);
   {
     float4* z = reinterpret_cast<float4*>(bt);
     const int n16 = (A.bt_bytes + 4 * A.acc_floats) >> 4;
@@ -293,8 +298,10 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_con
     gptr[threadIdx.x] = A.g[threadIdx.x].base + goff[threadIdx.x] + 2LL * A.offs_extra;
     gsm[threadIdx.x] = A.g[threadIdx.x].sm;
   }
-  stage_tables(bt, A.y, A.ybt, A.yR, A.ny, A.cg, cell);
-  stage_tables(bt, A.x, A.xbt, A.xR, A.nx, A.cg, cell);
+  if (product == 0)
+    stage_tables(bt, A.y, A.ybt, A.yR, A.ny, A.cg, cell);
+  else
+    stage_tables(bt, A.x, A.xbt, A.xR, A.nx, A.cg, cell);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // tables are read by the tensor core (async proxy)
   tc_fence_before();
   __syncthreads();
@@ -302,138 +309,134 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_con
   const uint32_t tbase = *tbase_s;
 
   {
-    // ------------------------------------------------ worker: half of one slab of every group of its set
-    const int h = warp >> 3, s = (warp >> 2) & 1, q = warp & 3;
+    // ------------------------------------------------ one slab of every group of the warp's set
+    const int s = warp >> 2, q = warp & 3;
     const uint32_t lanes = (uint32_t)(32 * q) << 16;
-    // tensor-memory columns of set s: A operand (hi 64, lo 64) at 256 s, accumulators P and Q at + 128, + 160
-    const uint32_t tAX = tbase + 256 * s + lanes, tAY = tAX;
-    const uint32_t tDX = tAX + 128, tDY = tAX + 160;
-    unsigned char* slot = ring + (4 * s + q) * kSlabBytes;
-    const uint32_t slot_u32 = smem_u32(slot);
-    const int pair_bar = 1 + 4 * s + q;  // named barrier of the two warps that share the slab
-    const int ngs = (A.ngroups - s + 1) >> 1;
-    uint32_t par_x = 0, par_y = 0;
+    // tensor-memory columns of set s: A operand of one K half (hi 32, lo 32) at 128 s, accumulators of the set's
+    // even / odd groups at + 64 / + 96
+    const uint32_t tA = tbase + 128 * s + lanes, tD = tA + 64;
+    const uint32_t slot_u32 = smem_u32(ring) + warp * kSlabBytes;
+    const uint32_t bt_u32 = smem_u32(bt), acc_u32 = smem_u32(acc);
+    const int ngs = (A.ngroups - s + 3) >> 2;
+    uint32_t par = 0;
     bool ok = true;
-    // cp.async chunk e = (8 h + i) * 32 + lane of the slab: row 2 (8 h + i) + (lane >> 4), 16-byte chunk lane & 15
-    const int pf_row0 = 16 * h + (lane >> 4), pf_c = (lane & 15) ^ (lane >> 4);
+    // lane-constant parts of the swizzled slot addresses: row-per-lane reads (P) and column-per-lane reads (Q)
+    const uint32_t xrd = slot_u32 + lane * 256, xsw = (lane & 15) << 4;
+    const uint32_t yrd = slot_u32 + ((lane & 1) << 3), ysw = (lane >> 1) << 4;
+    const int pf_hb = lane >> 4, pf_c = lane & 15;
 
-    auto prefetch = [&](const Work& w) {  // this warp's half of the slab into the ring slot
+    auto prefetch = [&](const Work& w) {  // the slab into the warp's ring slot, 16-byte chunks XOR-swizzled by row
       if (w.valid()) {
         const int n2tot = w.n2();
-        const float* src = gptr[w.ri()] + (long long)(w.r.y >> 8) * gsm[w.ri()] + 2LL * w.r.z +
-                           (long long)pf_row0 * 2 * n2tot + 4 * (lane & 15);
-        const uint32_t dst = slot_u32 + pf_row0 * 256;
+        const float* src = gptr[w.ri()] + (long long)(w.r.y >> 8) * gsm[w.ri()] + 2LL * w.r.z + (long long)pf_hb * 2 * n2tot + 4 * pf_c;
         const long long step = 4LL * n2tot;  // two rows, in floats
 #pragma unroll
-        for (int i = 0; i < 8; i++)  // row & 15 = (2 i + (lane >> 4)) & 15 (16 h drops out): chunk ^ row = pf_c ^ 2 i
-          cp_async16(dst + i * 512 + ((pf_c ^ (2 * i)) << 4), src + i * step);
+        for (int i = 0; i < 16; i++) {  // rows 2 i + pf_hb
+          const int row = 2 * i + pf_hb;
+          cp_async16(slot_u32 + row * 256 + ((pf_c ^ (row & 15)) << 4), src + i * step);
+        }
       }
       cp_async_commit();
     };
-    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory"); };
-    const uint32_t bt_u32 = smem_u32(bt), acc_u32 = smem_u32(acc);
-    // lane-constant parts of the swizzled slot addresses: row-per-lane reads and column-per-lane reads
-    const uint32_t xrd = slot_u32 + lane * 256, xsw = (lane & 15) << 4;
-    const uint32_t yrd = slot_u32 + ((lane & 1) << 3), ysw = (lane >> 1) << 4;
-    Work cur{}, next{};  // the previous group's record is re-read (from L1) where its accumulators are added
-    // the MMAs of the current group's products, by whichever warp completed their preconditions
-    auto issue_x = [&]() {
-      tc_fence_after();
-      issue_product(tAX - lanes, tDX - lanes, bt_u32 + cur.t.x, cur.t.y);
-      mma_commit(mdone_x + s);
+    // 32 of the slab's 64 K values of this lane's operand row: P: row n1 = lane, columns (n2, re/im) 32 half ..;
+    // Q: row n2 = lane, columns (n1, re/im) with n1 = 16 half ..
+    auto read_half = [&](int half, float (&v)[32]) {
+      if (product == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const float4 f = lds128(xrd + (((8 * half + i) << 4) ^ xsw));
+          v[4 * i] = f.x, v[4 * i + 1] = f.y, v[4 * i + 2] = f.z, v[4 * i + 3] = f.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+          const int n1 = 16 * half + i;
+          const float2 f = lds64(yrd + n1 * 256 + (((n1 & 15) << 4) ^ ysw));
+          v[2 * i] = f.x, v[2 * i + 1] = f.y;
+        }
+      }
     };
-    auto issue_y = [&]() {
-      tc_fence_after();
-      issue_product(tAY - lanes, tDY - lanes, bt_u32 + cur.t.z, cur.t.w);
-      mma_commit(mdone_y + s);
+    auto store_half = [&](const float (&v)[32]) {
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float t[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) t[i] = v[8 * j + i];
+        split_store8(tA, 8 * j, t);
+      }
+    };
+    Work cur{}, next{};
+    auto add_result = [&](int g) {  // the band of group g's accumulator to the gradient rows (record re-read from L1)
+      Work w;
+      load_work(A, g, q, lane, w);
+      if (w.valid()) {
+        const uint32_t tDg = tD + 32 * ((g >> 2) & 1);
+        if (product == 0)
+          epilogue<true>(tDg, acc_u32 + 4u * w.xacc(), w.n1(), w.a0() + lane, w.m(), w.l1(), w.l2(), w.cvec);
+        else
+          epilogue<false>(tDg, acc_u32 + 4u * w.yacc(), w.n2(), w.b0() + lane, w.m(), w.l1(), w.l2(), w.cvec);
+      }
+    };
+    auto arrive_and_issue = [&](int k, int half) {
+      tmem_wait_st();
+      tc_fence_before();
+      if (count_event(ev + s, 3)) {  // this warp completed the operand: the MMAs of the K half
+        tc_fence_after();
+        const uint32_t tDk = tD - lanes + 32 * (k & 1);
+        if (product == 0)
+          issue_half(tA - lanes, tDk, bt_u32 + cur.t.x, cur.t.y, half, half == 0);
+        else
+          issue_half(tA - lanes, tDk, bt_u32 + cur.t.z, cur.t.w, half, half == 0);
+        mma_commit(mdone + s);
+      }
     };
 
     if (ngs > 0) {
       load_work(A, s, q, lane, next);
       prefetch(next);
     }
-    bool have_prev = false;
-
-    // Per group: store the P operand; (upper warps) add the previous Q result while the P MMAs run; store the Q
-    // operand when the P MMAs have released the block; (lower warps) add the P result while the Q MMAs run.
-    // After a timeout (ok == false) the loop keeps its named barriers and arrivals but skips the work and the
-    // waits, so that the two warps of a pair never wait for each other in vain.
-    for (int k = 0; k < ngs; k++) {
+    // Per group: first K half of the operand, MMAs; second half read meanwhile, slot refilled, stored when the first
+    // MMAs have released the block, MMAs; the previous group's result is added while those run.
+    for (int k = 0; k < ngs && ok; k++) {
       cur = next;
-      if (k + 1 < ngs) load_work(A, s + 2 * (k + 1), q, lane, next);  // first used by the prefetch in step 3
+      if (k + 1 < ngs) load_work(A, s + 4 * (k + 1), q, lane, next);  // first used by the prefetch below
+      float v[32];
 
-      // 1. A operand of the P product: lane = row n1 of the slab, this warp's 32 of the 64 columns (n2, re/im)
       cp_async_wait_all();
-      pair_sync();
-      if (ok && cur.valid()) {
-#pragma unroll
-        for (int c2 = 0; c2 < 4; c2++) {
-          float v[8];
-#pragma unroll
-          for (int i = 0; i < 2; i++) {
-            const int c = 8 * h + 2 * c2 + i;
-            const float4 f = lds128(xrd + ((c << 4) ^ xsw));
-            v[4 * i] = f.x, v[4 * i + 1] = f.y, v[4 * i + 2] = f.z, v[4 * i + 3] = f.w;
-          }
-          split_store8(tAX, 32 * h + 8 * c2, v);
-        }
+      __syncwarp();
+      if (cur.valid()) {
+        read_half(0, v);
+        store_half(v);
       }
-      tmem_wait_st();
-      tc_fence_before();
-      if (count_event(evx + s, 7)) issue_x();
-
-      // 2. the upper warps add the Q result of the previous group (overlaps this group's P MMAs)
-      if (h == 1 && have_prev) {
-        Work prev;
-        load_work(A, s + 2 * (k - 1), q, lane, prev);
-        if (ok && prev.valid())
-          epilogue<false>(tDY, acc_u32 + 4u * prev.yacc(), prev.n2(), prev.b0() + lane, prev.m(), prev.l1(), prev.l2(), prev.cvec);
-      }
-
-      // 3. A operand of the Q product, once the P MMAs have consumed the previous contents: the slab
-      //    column-per-lane (lane = n2), this warp's 16 of the 32 rows n1 as columns (n1, re/im)
-      if (ok) ok = mbar_wait(mdone_x + s, par_x);
-      par_x ^= 1;
-      tc_fence_after();
-      if (ok && cur.valid()) {
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-          float v[8];
-#pragma unroll
-          for (int i = 0; i < 4; i++) {
-            const int n1 = 16 * h + 4 * j + i;
-            const float2 f = lds64(yrd + n1 * 256 + (((n1 & 15) << 4) ^ ysw));
-            v[2 * i] = f.x, v[2 * i + 1] = f.y;
-          }
-          split_store8(tAY, 32 * h + 8 * j, v);
-        }
-      }
-      pair_sync();  // both warps have read the slot: refill it with the next slab
+      arrive_and_issue(k, 0);
+      if (cur.valid()) read_half(1, v);
+      __syncwarp();  // every lane has read the slot: refill it with the next slab
       if (k + 1 < ngs) prefetch(next);
-      tmem_wait_st();
-      tc_fence_before();
-      if (count_event(evy + s, 7)) issue_y();
 
-      // 4. the lower warps add the P result (overlaps the Q MMAs)
-      if (ok && h == 0 && cur.valid())
-        epilogue<true>(tDX, acc_u32 + 4u * cur.xacc(), cur.n1(), cur.a0() + lane, cur.m(), cur.l1(), cur.l2(), cur.cvec);
-
-      // 5. the A block is free again when the Q MMAs are done
-      if (ok) ok = mbar_wait(mdone_y + s, par_y);
-      par_y ^= 1;
+      ok = mbar_wait(mdone + s, par);  // the first half's MMAs have consumed the block
+      par ^= 1;
+      if (!ok) break;
       tc_fence_after();
-      have_prev = true;
+      if (cur.valid()) store_half(v);
+      arrive_and_issue(k, 1);
+      if (k > 0) add_result(s + 4 * (k - 1));  // its accumulator is not touched before group k + 1
+
+      ok = mbar_wait(mdone + s, par);
+      par ^= 1;
+      if (!ok) break;
+      tc_fence_after();
     }
-    if (ok && h == 1 && have_prev && cur.valid())
-      epilogue<false>(tDY, acc_u32 + 4u * cur.yacc(), cur.n2(), cur.b0() + lane, cur.m(), cur.l1(), cur.l2(), cur.cvec);
+    if (ok && ngs > 0) add_result(s + 4 * (ngs - 1));
     cp_async_wait_all();
     if (!ok && lane == 0) *A.status = 1;
   }
 
   tc_fence_before();
   __syncthreads();
-  flush_rows(acc, A.xg, xgoff, A.xacc, A.nx, A.x_atomic != 0);
-  flush_rows(acc, A.yg, ygoff, A.yacc, A.ny, A.y_atomic != 0);
+  if (product == 0)
+    flush_rows(acc, A.xg, ogoff, A.xacc, A.nx, A.x_atomic != 0);
+  else
+    flush_rows(acc, A.yg, ogoff, A.yacc, A.ny, A.y_atomic != 0);
   if (warp == 0) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(512u) : "memory");
@@ -482,27 +485,30 @@ int launch_cg_bwd_tc(const VecCall& c, cudaStream_t s) {
     return GELIB_CUDA_ERROR;
   }
 
+  // Each CTA works on one product and holds only that product's tables and gradient rows: offsets of the y tables /
+  // x gradient rows (P) and of the x tables / y gradient rows (Q) both start at 0.
   TcArgs a;
-  int bt = 0, acc = 0;
+  int ybt = 0, xbt = 0, xacc = 0, yacc = 0;
   for (size_t i = 0; i < c.y.size(); i++) {
     a.y[i] = c.y[i];
     a.yg[i] = c.yg[i];
     a.yR[i] = round_up(2 * (2 * c.y[i].l + 1), 8);
-    a.ybt[i] = bt;
-    bt += (c.y[i].n / 32) * 512 * a.yR[i];
-    a.yacc[i] = acc;
-    acc += 2 * (2 * c.y[i].l + 1) * c.y[i].n;
+    a.ybt[i] = ybt;
+    ybt += (c.y[i].n / 32) * 512 * a.yR[i];
+    a.yacc[i] = yacc;
+    yacc += 2 * (2 * c.y[i].l + 1) * c.y[i].n;
   }
   for (size_t i = 0; i < c.x.size(); i++) {
     a.x[i] = c.x[i];
     a.xg[i] = c.xg[i];
     a.xR[i] = round_up(2 * (2 * c.x[i].l + 1), 8);
-    a.xbt[i] = bt;
-    bt += (c.x[i].n / 32) * 512 * a.xR[i];
-    a.xacc[i] = acc;
-    acc += 2 * (2 * c.x[i].l + 1) * c.x[i].n;
+    a.xbt[i] = xbt;
+    xbt += (c.x[i].n / 32) * 512 * a.xR[i];
+    a.xacc[i] = xacc;
+    xacc += 2 * (2 * c.x[i].l + 1) * c.x[i].n;
   }
-  bt += 512;  // an N = 32 read of a table with fewer rows runs into the next k-chunk: keep the last one in bounds
+  // + 512: an N = 32 read of a table with fewer rows runs into the next k-chunk: keep the last one in bounds
+  const int bt = round_up(std::max(xbt, ybt) + 512, 128), acc = std::max(xacc, yacc);
   for (size_t i = 0; i < c.r.size(); i++) a.g[i] = c.r[i];
   a.nx = (int)c.x.size();
   a.ny = (int)c.y.size();
@@ -512,12 +518,12 @@ int launch_cg_bwd_tc(const VecCall& c, cudaStream_t s) {
   const size_t smem = (size_t)kHeaderBytes + bt + 4 * (size_t)a.acc_floats + (size_t)kSlots * kSlabBytes;
   if (smem > 227 * 1024 || 4 * (size_t)a.acc_floats > 0xffff * 4) return -1;
 
-  std::vector<int> key = {7 /*family*/, (int)c.x.size(), (int)c.y.size(), (int)c.r.size()};
+  std::vector<int> key = {9 /*family*/, (int)c.x.size(), (int)c.y.size(), (int)c.r.size()};
   for (const auto& p : c.x) { key.push_back(p.l); key.push_back(p.n); }
   for (const auto& p : c.y) { key.push_back(p.l); key.push_back(p.n); }
   for (const auto& p : c.r) key.push_back(p.l);
   const auto xs = sig_of(c.x), ys = sig_of(c.y), rs = sig_of(c.r);
-  const int *xacc = a.xacc, *yacc = a.yacc, *xbt = a.xbt, *ybt = a.ybt, *xR = a.xR, *yR = a.yR;
+  const int *xaccp = a.xacc, *yaccp = a.yacc, *xbtp = a.xbt, *ybtp = a.ybt, *xR = a.xR, *yR = a.yR;
   DevicePlan* plan = get_plan(key, [&](DevicePlan& p) {
     build_schedule(xs, ys, rs, false, true, &p.sched);
     // slabs keyed by (xi, yi, a0, b0): they share both B operands
@@ -539,8 +545,8 @@ int launch_cg_bwd_tc(const VecCall& c, cudaStream_t s) {
       for (size_t i = 0; i < v.size(); i += 4) {
         const int ns = (int)std::min<size_t>(4, v.size() - i);
         p.h_items.push_back(make_int4(xi | (yi << 4) | (xs[xi].l << 8) | (ys[yi].l << 16), a0 | (b0 << 16),
-                                      xs[xi].n | (ys[yi].n << 16), xacc[xi] | (yacc[yi] << 16)));
-        p.h_items.push_back(make_int4(ybt[yi] + (b0 >> 5) * 512 * yR[yi], yR[yi], xbt[xi] + (a0 >> 5) * 512 * xR[xi], xR[xi]));
+                                      xs[xi].n | (ys[yi].n << 16), xaccp[xi] | (yaccp[yi] << 16)));
+        p.h_items.push_back(make_int4(ybtp[yi] + (b0 >> 5) * 512 * yR[yi], yR[yi], xbtp[xi] + (a0 >> 5) * 512 * xR[xi], xR[xi]));
         for (int j = 0; j < 4; j++) p.h_items.push_back(j < ns ? v[i + j] : make_int4(0, 0, 0, 0));
         for (int j = 0; j < 4; j++) {  // the band coefficients of the slab's row, zero-padded to 16
           float c[16] = {0};
@@ -560,7 +566,7 @@ int launch_cg_bwd_tc(const VecCall& c, cudaStream_t s) {
   });
   if (!plan) return GELIB_CUDA_ERROR;
   if (plan->nitems == 0 || c.cg.ncells == 0) return GELIB_OK;
-  if (c.cg.ncells > 0x7fffffffLL) return fail(GELIB_SKIPPED, fn, "number of cells exceeds 2^31-1");
+  if (c.cg.ncells > 0x3fffffffLL) return fail(GELIB_SKIPPED, fn, "number of cells exceeds 2^30-1");
 
   a.cg = c.cg;
   a.coeffs = plan->coeffs;
@@ -572,7 +578,7 @@ int launch_cg_bwd_tc(const VecCall& c, cudaStream_t s) {
   a.status = status;  // unified addressing: the host pointer of mapped memory is valid on the device
   cudaError_t e = cudaFuncSetAttribute(cg_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e == cudaSuccess) {
-    cg_bwd_tc_kernel<<<(unsigned)c.cg.ncells, kThreads, smem, s>>>(a);
+    cg_bwd_tc_kernel<<<(unsigned)(2 * c.cg.ncells), kThreads, smem, s>>>(a);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) return check_cuda(e, fn, "tensor-core backward kernel launch");
