@@ -86,7 +86,10 @@ def kernel_name(args, dom):
     if dom == "forward":
         tc = args.fwd_kernel == "tcgen05" or (args.fwd_kernel == "auto" and args.workload == "cfg3")
         return "cg_fwd_tc_kernel" if tc else "cg_fwd_kernel"
-    return "cg_bwd_tc_kernel" if args.bwd_kernel == "tcgen05" else "cg_bwd_kernel"
+    if args.bwd_kernel == "tcgen05":
+        return "cg_bwd_tc_kernel"
+    pair = args.bwd_kernel in ("auto", "pair") and args.workload in ("cfg1", "cfg2", "cfg3")
+    return "cg_bwd_pair_kernel" if pair else "cg_bwd_kernel"
 
 
 def measured_peak():
@@ -240,13 +243,12 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--bwd-kernel", default="simt", choices=["simt", "tcgen05"],
-                    help="backward kernel for channel counts that are multiples of 32: the default SIMT kernel or the tcgen05 one")
+    ap.add_argument("--bwd-kernel", default="auto", choices=["auto", "simt", "pair", "tcgen05"],
+                    help="backward kernel for channel counts that are multiples of 32 (auto = the pair kernel)")
     ap.add_argument("--fwd-kernel", default="auto", choices=["auto", "simt", "tcgen05"],
                     help="forward kernel for channel counts that are multiples of 32")
     args = ap.parse_args()
-    if args.bwd_kernel == "tcgen05":
-        os.environ["GELIB_B200_BWD"] = "tcgen05"
+    os.environ["GELIB_B200_BWD"] = args.bwd_kernel
     os.environ["GELIB_B200_FWD"] = args.fwd_kernel
     args.warmup = max(args.warmup, 0)
     desc, tx, ty, maxl, B, diag = WORKLOADS[args.workload]

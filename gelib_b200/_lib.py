@@ -62,6 +62,8 @@ SYMBOLS = {
     "gelib_SO3vec_addDiagCGproduct_back01": (ctypes.c_int, _VEC5),
     "gelib_SO3vec_addSPharm": (ctypes.c_int, [ctypes.c_int, _P5, _P5, ctypes.c_int, ctypes.c_void_p]),
     "gelib_kernel_launch_count": (ctypes.c_longlong, []),
+    "gelib_set_option": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_char_p]),
+    "gelib_async_status": (ctypes.c_int, []),
 }
 
 
@@ -84,6 +86,16 @@ def lib():
 
 def last_error():
     return lib().gelib_last_error().decode()
+
+
+def set_option(name, value):
+    """Pins the kernel choice ("fwd", "bwd") or a test switch ("inject_timeout"); see include/gelib_b200.h."""
+    check(lib().gelib_set_option(name.encode(), str(value).encode()))
+
+
+def async_status():
+    """Raises if a kernel with bounded waits gave up since the last check (call after synchronising)."""
+    check(lib().gelib_async_status())
 
 
 def check(status):

@@ -19,6 +19,15 @@ def _ints(v):
     return (ctypes.c_int * max(1, len(v)))(*v)
 
 
+def _one_device(*tensors):
+    """The reference asserts that the operands of a product live on one device (SO3/SO3part.hpp:351,
+    core/CGproduct.hpp:47-49); here a tensor on another GPU would be dereferenced as a raw pointer."""
+    dev = tensors[0].device
+    for t in tensors:
+        if t.device != dev:
+            raise RuntimeError("GElib error: operands on different devices (%s and %s)." % (dev, t.device))
+
+
 class SO3type:
     """The type of an SO3vec: l -> number of channels.  python/bindings/SO3type_py.cpp:16-43."""
 
@@ -96,31 +105,33 @@ class SO3part:
         return self.t.size(-1)
 
     def _call3(self, name, a, b, c, offs, flags=0):
+        _one_device(a, b, c)
         with device_guard(a):
             da, db, dc = descriptor(a), descriptor(b), descriptor(c)
             return check(getattr(lib(), name)(ctypes.byref(da), ctypes.byref(db), ctypes.byref(dc), offs, flags,
                                               stream_of(a)))
 
     def add_CGproduct(self, x, y, offs=0, *, overwrite=False):
-        self._call3("gelib_SO3part_addCGproduct", self.t, x.t, y.t, offs, GELIB_OVERWRITE if overwrite else 0)
+        return self._call3("gelib_SO3part_addCGproduct", self.t, x.t, y.t, offs, GELIB_OVERWRITE if overwrite else 0)
 
     def add_CGproduct_back0(self, g, y, offs=0):
-        self._call3("gelib_SO3part_addCGproduct_back0", self.t, g.t, y.t, offs)
+        return self._call3("gelib_SO3part_addCGproduct_back0", self.t, g.t, y.t, offs)
 
     def add_CGproduct_back1(self, g, x, offs=0):
-        self._call3("gelib_SO3part_addCGproduct_back1", self.t, g.t, x.t, offs)
+        return self._call3("gelib_SO3part_addCGproduct_back1", self.t, g.t, x.t, offs)
 
     def add_DiagCGproduct(self, x, y, offs=0, *, overwrite=False):
-        self._call3("gelib_SO3part_addDiagCGproduct", self.t, x.t, y.t, offs, GELIB_OVERWRITE if overwrite else 0)
+        return self._call3("gelib_SO3part_addDiagCGproduct", self.t, x.t, y.t, offs, GELIB_OVERWRITE if overwrite else 0)
 
     def add_DiagCGproduct_back0(self, g, y, offs=0):
-        self._call3("gelib_SO3part_addDiagCGproduct_back0", self.t, g.t, y.t, offs)
+        return self._call3("gelib_SO3part_addDiagCGproduct_back0", self.t, g.t, y.t, offs)
 
     def add_DiagCGproduct_back1(self, g, x, offs=0):
-        self._call3("gelib_SO3part_addDiagCGproduct_back1", self.t, g.t, x.t, offs)
+        return self._call3("gelib_SO3part_addDiagCGproduct_back1", self.t, g.t, x.t, offs)
 
     @staticmethod
     def _back01(name, xg, yg, g, x, y, offs):
+        _one_device(xg.t, yg.t, g.t, x.t, y.t)
         with device_guard(g.t):
             d = [descriptor(v.t) for v in (xg, yg, g, x, y)]
             return check(getattr(lib(), name)(*[ctypes.byref(v) for v in d], offs, 0, stream_of(g.t)))
@@ -128,16 +139,17 @@ class SO3part:
     @staticmethod
     def add_CGproduct_back01(xg, yg, g, x, y, offs=0):
         """Both gradients from one pass over g (fused back0 + back1)."""
-        SO3part._back01("gelib_SO3part_addCGproduct_back01", xg, yg, g, x, y, offs)
+        return SO3part._back01("gelib_SO3part_addCGproduct_back01", xg, yg, g, x, y, offs)
 
     @staticmethod
     def add_DiagCGproduct_back01(xg, yg, g, x, y, offs=0):
-        SO3part._back01("gelib_SO3part_addDiagCGproduct_back01", xg, yg, g, x, y, offs)
+        return SO3part._back01("gelib_SO3part_addDiagCGproduct_back01", xg, yg, g, x, y, offs)
 
     def add_spharm(self, X, *, overwrite=False):
         """self += Y_l(X) for X (batch, [grid...], 3, channels) float32, or (3, channels) broadcast over the batch."""
         if X.dim() == 2:
             X = X.unsqueeze(0)
+        _one_device(self.t, X)
         with device_guard(self.t):
             dr, dx = descriptor(self.t), descriptor(X, real=True)
             check(lib().gelib_SO3part_addSPharm(ctypes.byref(dr), ctypes.byref(dx), GELIB_OVERWRITE if overwrite else 0,
@@ -174,33 +186,37 @@ class SO3vec:
         ta, tb, tc = a._tensors(), b._tensors(), c._tensors()
         if not ta or not tb or not tc:
             return True
+        _one_device(*(ta + tb + tc))
         with device_guard(ta[0]):
             return check(getattr(lib(), name)(len(ta), descriptor_array(ta), len(tb), descriptor_array(tb), len(tc),
                                               descriptor_array(tc), flags, stream_of(ta[0])))
 
     def addCGproduct(self, x, y, *, overwrite=False):
-        self._call3("gelib_SO3vec_addCGproduct", self, x, y, GELIB_OVERWRITE if overwrite else 0)
+        return self._call3("gelib_SO3vec_addCGproduct", self, x, y, GELIB_OVERWRITE if overwrite else 0)
 
     def addCGproduct_back0(self, g, y):
-        self._call3("gelib_SO3vec_addCGproduct_back0", self, g, y)
+        return self._call3("gelib_SO3vec_addCGproduct_back0", self, g, y)
 
     def addCGproduct_back1(self, g, x):
-        self._call3("gelib_SO3vec_addCGproduct_back1", self, g, x)
+        return self._call3("gelib_SO3vec_addCGproduct_back1", self, g, x)
 
     def addDiagCGproduct(self, x, y, *, overwrite=False):
-        self._call3("gelib_SO3vec_addDiagCGproduct", self, x, y, GELIB_OVERWRITE if overwrite else 0)
+        return self._call3("gelib_SO3vec_addDiagCGproduct", self, x, y, GELIB_OVERWRITE if overwrite else 0)
 
     def addDiagCGproduct_back0(self, g, y):
-        self._call3("gelib_SO3vec_addDiagCGproduct_back0", self, g, y)
+        return self._call3("gelib_SO3vec_addDiagCGproduct_back0", self, g, y)
 
     def addDiagCGproduct_back1(self, g, x):
-        self._call3("gelib_SO3vec_addDiagCGproduct_back1", self, g, x)
+        return self._call3("gelib_SO3vec_addDiagCGproduct_back1", self, g, x)
 
     @staticmethod
     def _back01(name, xg, yg, g, x, y):
         txg, tyg, tg, tx, ty = (v._tensors() for v in (xg, yg, g, x, y))
         if not tg or not tx or not ty:
             return True
+        if len(txg) != len(tx) or len(tyg) != len(ty):
+            raise RuntimeError("GElib error: gradient vectors must have the parts of x and y.")
+        _one_device(*(txg + tyg + tg + tx + ty))
         with device_guard(tg[0]):
             return check(getattr(lib(), name)(len(txg), descriptor_array(txg), len(tyg), descriptor_array(tyg),
                                               len(tg), descriptor_array(tg), descriptor_array(tx),
@@ -209,17 +225,18 @@ class SO3vec:
     @staticmethod
     def addCGproduct_back01(xg, yg, g, x, y):
         """Both gradients of the full product from one pass over g."""
-        SO3vec._back01("gelib_SO3vec_addCGproduct_back01", xg, yg, g, x, y)
+        return SO3vec._back01("gelib_SO3vec_addCGproduct_back01", xg, yg, g, x, y)
 
     @staticmethod
     def addDiagCGproduct_back01(xg, yg, g, x, y):
-        SO3vec._back01("gelib_SO3vec_addDiagCGproduct_back01", xg, yg, g, x, y)
+        return SO3vec._back01("gelib_SO3vec_addDiagCGproduct_back01", xg, yg, g, x, y)
 
     def add_spharm(self, X, *, overwrite=False):
         """Every part += its spherical harmonics of X, from one Legendre recursion per point."""
         tr = self._tensors()
         if X.dim() == 2:
             X = X.unsqueeze(0)
+        _one_device(*(tr + [X]))
         with device_guard(tr[0]):
             dx = descriptor(X, real=True)
             check(lib().gelib_SO3vec_addSPharm(len(tr), descriptor_array(tr), ctypes.byref(dx),

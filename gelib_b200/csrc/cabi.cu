@@ -35,6 +35,14 @@ int parse_parts(const char* fn, const char* name, int n, const gelib_tensor5* t,
       if (t[i].dims[d] == 0) empty = true;
     }
     if (!t[i].base && !empty) return fail(GELIB_INVALID, fn, std::string("null data pointer in ") + name);
+    if (!real3 && !empty) {
+      // complex data is read and written as (re, im) pairs with 8-byte accesses
+      if ((uintptr_t)t[i].base % 8 != 0)
+        return fail(GELIB_INVALID, fn, std::string("data pointer of ") + name + " is not 8-byte aligned");
+      for (int d = 0; d < 5; d++)
+        if (t[i].dims[d] > 1 && t[i].strides[d] % 2 != 0)
+          return fail(GELIB_INVALID, fn, std::string("odd stride (in floats) in complex tensor ") + name);
+    }
     if (!real3 && t[i].dims[3] % 2 == 0)
       return fail(GELIB_SKIPPED, fn, std::string("dims[3] of ") + name + " is not of the form 2l+1");
     order.push_back({real3 ? 0 : (t[i].dims[3] - 1) / 2, i});
@@ -133,6 +141,8 @@ int run_product(const char* fn, bool diag, int mode, int nr, const gelib_tensor5
   c.offs_extra = offs;
   std::vector<const gelib_tensor5*> sr, sx, sy, sxg, syg;
   int st;
+  // a kernel of an earlier call whose bounded wait ran out is reported here, whatever this call would run
+  if ((st = poll_async_status(fn)) != GELIB_OK) return st;
   if ((st = parse_parts(fn, "r", nr, r, false, &c.r, &sr)) != GELIB_OK) return st;
   if (mode == 0 || mode == 2 || mode == 3)
     if ((st = parse_parts(fn, "x", nx, x, false, &c.x, &sx)) != GELIB_OK) return st;
@@ -186,7 +196,13 @@ int run_product(const char* fn, bool diag, int mode, int nr, const gelib_tensor5
     if (!aligned16(p)) c.vec_ok = false;
   for (const auto& p : c.y)
     if (p.n % 2) c.vec_ok = false;
+  c.in_vec_ok = true;
+  for (auto* v : {&c.x, &c.y, &c.xg, &c.yg})
+    for (const auto& p : *v)
+      if (!aligned16(p)) c.in_vec_ok = false;
   if (c.cg.ncells == 0) return GELIB_OK;
+  if (mode == 0 && c.r_bcast && (flags & GELIB_OVERWRITE))
+    return fail(GELIB_INVALID, fn, "GELIB_OVERWRITE with an output that is broadcast over cells (the cells are summed into it)");
 
   cudaStream_t s = (cudaStream_t)stream;
   if (mode == 0) {
@@ -265,6 +281,10 @@ int gelib_CGmatrix(int l1, int l2, int l, float* out) {
 
 int gelib_SO3type_CGproduct(int nx, const int* xl, const int* xn, int ny, const int* yl, const int* yn, int maxl,
                             int diag, int cap, int* out_l, int* out_n) {
+  if (nx < 0 || ny < 0 || cap < 0 || (nx > 0 && (!xl || !xn)) || (ny > 0 && (!yl || !yn)) || (cap > 0 && (!out_l || !out_n)))
+    return -2;
+  for (int i = 0; i < nx; i++) if (xl[i] < 0 || xn[i] < 0) return -2;
+  for (int i = 0; i < ny; i++) if (yl[i] < 0 || yn[i] < 0) return -2;
   std::map<int, long long> R;
   type_product(nx, xl, xn, ny, yl, yn, maxl, diag != 0, &R);
   if ((int)R.size() > cap) return -1;
@@ -279,6 +299,12 @@ int gelib_SO3type_CGproduct(int nx, const int* xl, const int* xn, int ny, const 
 
 int gelib_SO3vec_CGproduct_schedule(int nx, const int* xl, const int* xn, int ny, const int* yl, const int* yn, int nr,
                                     const int* rl, int diag, int cap, int* out) {
+  if (nx < 0 || ny < 0 || nr < 0 || cap < 0 || (nx > 0 && (!xl || !xn)) || (ny > 0 && (!yl || !yn)) || (nr > 0 && !rl) ||
+      (cap > 0 && !out))
+    return -2;
+  for (int i = 0; i < nx; i++) if (xl[i] < 0 || xn[i] < 0) return -2;
+  for (int i = 0; i < ny; i++) if (yl[i] < 0 || yn[i] < 0) return -2;
+  for (int i = 0; i < nr; i++) if (rl[i] < 0) return -2;
   std::vector<PartSig> xs, ys, rs;
   for (int i = 0; i < nx; i++) xs.push_back({xl[i], xn[i]});
   for (int i = 0; i < ny; i++) ys.push_back({yl[i], yn[i]});
@@ -402,5 +428,13 @@ int gelib_SO3part_addSPharm(const gelib_tensor5* r, const gelib_tensor5* x, int 
 }
 
 long long gelib_kernel_launch_count(void) { return launch_count(); }
+
+int gelib_set_option(const char* name, const char* value) {
+  const int st = set_option(name, value);
+  if (st != GELIB_OK) return fail(GELIB_INVALID, "gelib_set_option", "unknown option name or value");
+  return GELIB_OK;
+}
+
+int gelib_async_status(void) { return poll_async_status("gelib_async_status"); }
 
 }  // extern "C"

@@ -345,15 +345,20 @@ inline int align4(int v) { return (v + 3) / 4 * 4; }
 
 int launch_cg_bwd(const VecCall& c, cudaStream_t s) {
   static const char* fn = "SO3vec_addCGproduct_back";
-  // GELIB_B200_BWD=tcgen05 sends calls that qualify (channel counts that are multiples of 32, both gradients
-  // requested) to the tensor-core kernel of cg_bwd_tc.cu; "tcgen05!" refuses calls that do not qualify instead of
-  // falling back (tests use it to be sure which kernel ran).  The default is this file's kernel, which measured
-  // about 2 % faster on the headline shapes.
-  const char* which = getenv("GELIB_B200_BWD");
-  if (which && (std::string(which) == "tcgen05" || std::string(which) == "tcgen05!")) {
+  // Calls whose channel counts are multiples of 32 go to the uncoupled-gradient kernel of cg_bwd_pair.cu (about
+  // 0.6 of this file's kernel's instructions per band entry); everything else stays here.  Option "bwd" (initially
+  // GELIB_B200_BWD): "simt" keeps everything on this file's kernel, "pair" / "tcgen05" name the kernel to try first,
+  // and with a trailing "!" a call that does not qualify for it is refused instead of falling back (tests use that
+  // to be sure which kernel ran).
+  const int mode = bwd_mode();
+  if (mode == kBwdTc || mode == kBwdTcStrict) {
     const int rc = launch_cg_bwd_tc(c, s);
     if (rc != -1) return rc;
-    if (std::string(which) == "tcgen05!") return fail(GELIB_INVALID, fn, "the call does not qualify for the tcgen05 kernel");
+    if (mode == kBwdTcStrict) return fail(GELIB_INVALID, fn, "the call does not qualify for the tcgen05 kernel");
+  } else if (mode != kBwdSimt) {
+    const int rc = launch_cg_bwd_pair(c, s);
+    if (rc != -1) return rc;
+    if (mode == kBwdPairStrict) return fail(GELIB_INVALID, fn, "the call does not qualify for the pair kernel");
   }
   const bool vec = c.vec_ok;
   const int UB = vec ? 2 : 1;

@@ -1,0 +1,492 @@
+// Backward Clebsch-Gordan product through the uncoupled gradient of each (l1,l2) pair: both gradients of every
+// triple from ONE read of g, for channel counts that are multiples of 32.  Default backward kernel for such calls.
+//
+//   xg_l1[cell, m1, n1] += sum_{l,m2,n2} C_l[m1,m2] g_l[cell, m1+m2, offs_l + n1*N2 + n2] conj(y_l2[cell, m2, n2])
+//   yg_l2[cell, m2, n2] += sum_{l,m1,n1} C_l[m1,m2] g_l[cell, m1+m2, offs_l + n1*N2 + n2] conj(x_l1[cell, m1, n1])
+//
+// Replaces SO3part_addCGproduct_back0_kernel / _back1_kernel and their launchers
+// (cuda/SO3part_addCGproduct_back0.cu:32-294, cuda/SO3part_addCGproduct_back1.cu:32-175 of GElib), which read g
+// twice, and the launch-per-triple loops Gvec::add_CGproduct_back0 / _back1 (core/Gvec.hpp:323-345).
+//
+// Arithmetic.  For a fixed pair (l1,l2) and a fixed row m = m1+m2, every output l >= |m| of the pair meets the SAME
+// band of (m1,m2) and the same rows x[m1], y[m2]; only the coefficient differs.  So the kernel first forms, per band
+// entry, the uncoupled gradient  H[n1][n2] = sum_l C_l[m1,m2] g_l[m][n1][n2]  (one real multiply-add per float) and
+// contracts H with conj(y[m2]) and conj(x[m1]) once, instead of contracting every g_l separately: at maxl 6 that is
+// 7651 combinations + 2149 contractions per cell in place of 7651 contractions (0.78 of the multiply-adds, 0.28 of
+// the operand-row reads).
+//
+// Organisation.  One CTA per cell; x and y rows and the gradient accumulators of the cell live in shared memory.
+// A producer warp walks a list of groups -- (pair, 32 x 32 channel tile, row m, up to four output l) -- and brings
+// the slabs g_l[m] of a group (32 rows of 256 bytes each), the group's coefficients and its two consumer descriptors
+// into a four-stage ring with 16-byte asynchronous copies (cp.async, completion counted on an mbarrier; slab rows
+// padded to 272 bytes so both read patterns are conflict-free; one bulk copy per row was tried first and was
+// bound by the copy engine's rate of 256-byte requests).
+// Eight consumer warps share every group: warps 0-3 produce xg (lane = n1, each warp one quarter of n2, so the sum
+// over n2 stays inside a lane), warps 4-7 produce yg (lane = n2, each warp one quarter of n1).  A warp copies its
+// quarter of each slab into registers and loops over the band, two entries at a time; the running sums for every m1
+// (resp. m2) of the pair live in a private shared-memory block of the warp (one 8-byte slot per lane and row: plain
+// load / add / store, conflict-free) until the pair-tile ends, then go to the CTA's accumulators with one atomic per
+// value.  No shuffles, no atomics inside the band loop, no CTA-wide barrier between groups.  The four warps of a role add into the same accumulator in no fixed
+// order, so gradients are reproducible to rounding (about 1e-7 relative), not bitwise.
+//
+// Every wait on an mbarrier is bounded; on a timeout the kernel records it in a host-mapped status word, leaves its
+// loops, lets its copies in flight land, and returns; the C ABI reports the failure on the next call.
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <string>
+
+#include "plan.h"
+#include "tc_common.h"
+
+namespace gelib_b200 {
+
+namespace {
+
+using namespace tc;
+
+constexpr int kConsumers = 8;                        // 2 roles x 4 quarter tiles
+constexpr int kThreads = (kConsumers + 1) * 32;      // + the producer warp
+constexpr int kRowPitch = 272;                       // bytes per staged slab row: 32 complex + 16
+constexpr int kSlotBytes = 32 * kRowPitch;           // one slab
+constexpr int kGroupSlabs = 4;                       // slabs per group
+constexpr int kMaxBand = 17;                         // band entries per group: 2*8+1
+constexpr int kCoefOff = kGroupSlabs * kSlotBytes;   // one coefficient quad per band entry
+constexpr int kDescOff = kCoefOff + kMaxBand * 16;   // the two consumer descriptors (32 bytes each)
+constexpr int kStageBytes = kDescOff + 64 + 48;      // 128 | size
+constexpr int kMaxStages = 4;
+constexpr int kHeaderBytes = 512;                    // mbarriers, cell offsets
+constexpr int kRec = 7;                              // int4 per group record
+static_assert(kStageBytes % 128 == 0, "stages stay 128-byte aligned");
+
+struct PairArgs {
+  PartView x[kMaxParts], y[kMaxParts], g[kMaxParts], xg[kMaxParts], yg[kMaxParts];
+  int xoff[kMaxParts], yoff[kMaxParts];  // float offsets of the staged parts inside the cell block
+  int nx, ny, ng;
+  int cell_floats;                       // staged floats per cell (the accumulators use the same layout)
+  int nstages;
+  CellGrid cg;
+  // seven int4 per group.  [0..1] descriptor of the xg warps, [2..3] of the yg warps:
+  //   {nslab | band length<<8 | last<<16 | accumulator rows of the pair<<24,
+  //    byte offset in shared memory of the other operand's row for the first band entry (tile column 0),
+  //    its signed step in bytes, accumulator row of the first entry, its step (+1 / -1),
+  //    float offset of the pair-tile's rows in the CTA accumulators, their pitch in floats, 0}
+  // [4..6] for the producer:
+  //   {nslab | band length<<8 | n2<<16, index of the first coefficient quad, 4 x {ri | (m+l)<<8, first channel of the
+  //    tile inside part ri}, 0, 0}
+  const int4* recs;
+  int ngroups;
+  const float4* coef;                    // per band entry the coefficients of the group's slabs, zero-padded to 4
+  int offs_extra;
+  int do_x, do_y, x_atomic, y_atomic;
+  int skip_group;                        // test hook: the producer never signals this group (-1: none)
+  int* status;                           // host-mapped; set to 1 when a wait ran out
+};
+
+// The mbarrier gets one arrival from this thread once all cp.async it has issued so far have landed (the count the
+// barrier was initialised with already includes it).
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// H = sum_l c_l G_l for the warp's 8 complex numbers, contracted with the conjugate of the other operand's 8.
+template <int LM>
+__device__ __forceinline__ void contract(const float (&G)[kGroupSlabs][16], const float4 c, const float4 (&w)[4], float& sr,
+                                         float& si) {
+  const float v[16] = {w[0].x, w[0].y, w[0].z, w[0].w, w[1].x, w[1].y, w[1].z, w[1].w,
+                       w[2].x, w[2].y, w[2].z, w[2].w, w[3].x, w[3].y, w[3].z, w[3].w};
+  float H[16];
+#pragma unroll
+  for (int e = 0; e < 16; e++) {
+    if (LM == 1) {
+      H[e] = G[0][e];
+    } else {
+      float h = c.x * G[0][e];
+      h = fmaf(c.y, G[1][e], h);
+      if (LM > 2) h = fmaf(c.z, G[2][e], h);
+      if (LM > 3) h = fmaf(c.w, G[3][e], h);
+      H[e] = h;
+    }
+  }
+  float sr0 = 0.f, si0 = 0.f, sr1 = 0.f, si1 = 0.f;
+#pragma unroll
+  for (int e = 0; e < 16; e += 4) {
+    sr0 = fmaf(H[e], v[e], sr0);
+    si0 = fmaf(H[e + 1], v[e], si0);
+    sr1 = fmaf(H[e + 2], v[e + 2], sr1);
+    si1 = fmaf(H[e + 3], v[e + 2], si1);
+    sr0 = fmaf(H[e + 1], v[e + 1], sr0);
+    si0 = fmaf(-H[e], v[e + 1], si0);
+    sr1 = fmaf(H[e + 3], v[e + 3], sr1);
+    si1 = fmaf(-H[e + 2], v[e + 3], si1);
+  }
+  sr = sr0 + sr1;
+  si = si0 + si1;
+  if (LM == 1) {
+    sr *= c.x;
+    si *= c.x;
+  }
+}
+
+// The band of one group for one warp, two entries per trip so that the loads of one hide behind the arithmetic of the
+// other.  G: the warp's quarter of the group's slabs; coef: the group's coefficient quads; o: the other operand's row
+// chunk for the first entry (4 x 16 bytes), ostep its signed step in 16-byte units; a: the lane's slot in the warp's
+// private accumulator row of the first entry, astep its signed step in 8-byte units.
+template <int LM>
+__device__ __forceinline__ void band_loop(const float (&G)[kGroupSlabs][16], const float4* coef, int cnt, const float4* o,
+                                          int ostep, float2* a, int astep) {
+  int k = 0;
+  for (; k + 1 < cnt; k += 2) {
+    const float4 c0 = coef[k], c1 = coef[k + 1];
+    const float4* o1 = o + ostep;
+    float2* a1 = a + astep;
+    const float4 w0[4] = {o[0], o[1], o[2], o[3]};
+    const float4 w1[4] = {o1[0], o1[1], o1[2], o1[3]};
+    float2 s0 = *a, s1 = *a1;
+    float r0, i0, r1, i1;
+    contract<LM>(G, c0, w0, r0, i0);
+    contract<LM>(G, c1, w1, r1, i1);
+    s0.x += r0; s0.y += i0;
+    s1.x += r1; s1.y += i1;
+    *a = s0;
+    *a1 = s1;
+    o = o1 + ostep;
+    a = a1 + astep;
+  }
+  if (k < cnt) {
+    const float4 c0 = coef[k];
+    const float4 w0[4] = {o[0], o[1], o[2], o[3]};
+    float2 s0 = *a;
+    float r0, i0;
+    contract<LM>(G, c0, w0, r0, i0);
+    s0.x += r0; s0.y += i0;
+    *a = s0;
+  }
+}
+
+__device__ __forceinline__ void stage_parts(float* dst_cell, const PartView* parts, const int* off, int nparts,
+                                            const CellGrid& cg, long long cell) {
+  for (int i = 0; i < nparts; i++) {
+    const PartView& p = parts[i];
+    const float* src = p.base + cell_offset(p, cg, cell);
+    float* dst = dst_cell + off[i];
+    const int n = p.n, total = (2 * p.l + 1) * n;
+    for (int e = threadIdx.x; e < total; e += blockDim.x) {
+      const int m = e / n, ch = e - m * n;
+      *reinterpret_cast<float2*>(dst + 2 * e) = __ldg(reinterpret_cast<const float2*>(src + (long long)m * p.sm + 2 * ch));
+    }
+  }
+}
+
+__device__ __forceinline__ void flush_rows(const float* acc_cell, const PartView* out, const long long* cell_off,
+                                           const int* off, int nparts, bool atomic) {
+  for (int i = 0; i < nparts; i++) {
+    const PartView& p = out[i];
+    const int n = p.n, total = (2 * p.l + 1) * n;
+    for (int e = threadIdx.x; e < total; e += blockDim.x) {
+      const int row = e / n, ch = e - row * n;
+      const float2 v = *reinterpret_cast<const float2*>(acc_cell + off[i] + 2 * e);
+      float* dst = p.base + cell_off[i] + (long long)row * p.sm + 2 * ch;
+      if (atomic) {
+        atomicAdd(dst, v.x);
+        atomicAdd(dst + 1, v.y);
+      } else {
+        float2 o = *reinterpret_cast<float2*>(dst);
+        o.x += v.x;
+        o.y += v.y;
+        *reinterpret_cast<float2*>(dst) = o;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_constant__ PairArgs A, const int J) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw);           // [kMaxStages]
+  uint64_t* empty = full + kMaxStages;                               // [kMaxStages]
+  long long* goff = reinterpret_cast<long long*>(smem_raw + 128);    // [kMaxParts] cell offsets into the g parts
+  long long* xgoff = goff + kMaxParts;
+  long long* ygoff = xgoff + kMaxParts;
+  float* stage_f = reinterpret_cast<float*>(smem_raw + kHeaderBytes);   // staged x,y rows of the cell
+  float* acc_f = stage_f + A.cell_floats;                               // gradient accumulators, same layout
+  float2* priv = reinterpret_cast<float2*>(acc_f + A.cell_floats);      // [kConsumers][J][32] private partial rows
+  const int ring_off = (kHeaderBytes + 8 * A.cell_floats + kConsumers * J * 256 + 127) & ~127;
+  unsigned char* ring = smem_raw + ring_off;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long cell = blockIdx.x;
+  const int NS = A.nstages;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NS; s++) {
+      mbar_init(&full[s], 32);          // one arrival per producer lane, when that lane's copies have landed
+      mbar_init(&empty[s], kConsumers);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int e = threadIdx.x; e < A.ng; e += blockDim.x) goff[e] = cell_offset(A.g[e], A.cg, cell);
+  if (A.do_x)
+    for (int e = threadIdx.x; e < A.nx; e += blockDim.x) xgoff[e] = cell_offset(A.xg[e], A.cg, cell);
+  if (A.do_y)
+    for (int e = threadIdx.x; e < A.ny; e += blockDim.x) ygoff[e] = cell_offset(A.yg[e], A.cg, cell);
+  stage_parts(stage_f, A.x, A.xoff, A.nx, A.cg, cell);
+  stage_parts(stage_f, A.y, A.yoff, A.ny, A.cg, cell);
+  for (int e = threadIdx.x; e < A.cell_floats + kConsumers * J * 64; e += blockDim.x) acc_f[e] = 0.f;  // + priv
+  __syncthreads();
+
+  if (warp == kConsumers) {
+    // ---- producer: 16-byte asynchronous copies, a group per stage.  Lane t moves chunk t of two rows at a time
+    // (global reads of 512 contiguous bytes per instruction), 16 instructions per slab.
+    bool ok = true;
+    int4 p0 = make_int4(0, 0, 0, 0), p1 = p0, p2 = p0;
+    if (A.ngroups > 0) {
+      p0 = __ldg(&A.recs[4]); p1 = __ldg(&A.recs[5]); p2 = __ldg(&A.recs[6]);
+    }
+    const int half = lane >> 4, cc = lane & 15;
+    const uint32_t ring_a = smem_u32(ring);
+    for (int gi = 0; gi < A.ngroups; gi++) {
+      const int st = gi % NS, round = gi / NS;
+      // the next record is on its way while this group is issued
+      const int gn = gi + 1 < A.ngroups ? gi + 1 : gi;
+      const int4 n0 = __ldg(&A.recs[kRec * gn + 4]), n1 = __ldg(&A.recs[kRec * gn + 5]), n2r = __ldg(&A.recs[kRec * gn + 6]);
+      if (round > 0) ok = mbar_wait(&empty[st], (round - 1) & 1);
+      if (!ok) break;
+      const int nslab = p0.x & 7, cnt = (p0.x >> 8) & 0xff, n2 = (p0.x >> 16) & 0xffff;
+      const uint32_t sbase = ring_a + st * kStageBytes;
+      const int sw[8] = {p0.z, p0.w, p1.x, p1.y, p1.z, p1.w, p2.x, p2.y};
+#pragma unroll
+      for (int s = 0; s < kGroupSlabs; s++) {
+        if (s < nslab) {
+          const int ri = sw[2 * s] & 0xff, row = sw[2 * s] >> 8;
+          const PartView& gp = A.g[ri];
+          const float* src = gp.base + goff[ri] + (long long)row * gp.sm +
+                             2LL * ((long long)sw[2 * s + 1] + A.offs_extra + (long long)half * n2) + 4 * cc;
+          const uint32_t dst = sbase + s * kSlotBytes + half * kRowPitch + cc * 16;
+          const long long step = 4LL * n2;  // two rows of the part, in floats
+#pragma unroll
+          for (int it = 0; it < 16; it++) cp_async16(dst + it * 2 * kRowPitch, src + it * step);
+        }
+      }
+      if (lane < cnt) cp_async16(sbase + kCoefOff + lane * 16, A.coef + p0.y + lane);
+      if (lane < 4) cp_async16(sbase + kDescOff + lane * 16, &A.recs[kRec * gi + lane]);
+      if (gi != A.skip_group) cp_async_arrive(&full[st]);
+      p0 = n0; p1 = n1; p2 = n2r;
+    }
+    cp_async_wait_all();  // nothing of this warp is in flight when the CTA gives its shared memory back
+    if (!ok && lane == 0) *A.status = 1;
+  } else {
+    // ---- consumers
+    const int role = warp >> 2, q = warp & 3;
+    const bool active = role == 0 ? (A.do_x != 0) : (A.do_y != 0);
+    float2* mine = priv + (warp * J) * 32 + lane;
+    // where the warp's quarter of a slab sits inside a slot: xg warps read row `lane`, columns 8q..8q+7 (16-byte
+    // loads, lanes 272 bytes apart); yg warps read rows 8q..8q+7, column `lane` (8-byte loads, lanes adjacent)
+    const int goffs = role == 0 ? lane * kRowPitch + q * 64 : 8 * q * kRowPitch + lane * 8;
+    bool ok = true;
+    for (int gi = 0; gi < A.ngroups; gi++) {
+      const int st = gi % NS, round = gi / NS;
+      ok = mbar_wait(&full[st], round & 1);
+      if (!ok) break;
+      if (active) {
+        const unsigned char* sbase = ring + st * kStageBytes;
+        const int4 d0 = *reinterpret_cast<const int4*>(sbase + kDescOff + role * 32);
+        const int4 d1 = *reinterpret_cast<const int4*>(sbase + kDescOff + role * 32 + 16);
+        const int nslab = d0.x & 7, cnt = (d0.x >> 8) & 0xff;
+        float G[kGroupSlabs][16];
+        if (role == 0) {
+#pragma unroll
+          for (int s = 0; s < kGroupSlabs; s++) {
+            if (s < nslab) {
+              const float4* gp = reinterpret_cast<const float4*>(sbase + s * kSlotBytes + goffs);
+#pragma unroll
+              for (int t = 0; t < 4; t++) {
+                const float4 w = gp[t];
+                G[s][4 * t] = w.x; G[s][4 * t + 1] = w.y; G[s][4 * t + 2] = w.z; G[s][4 * t + 3] = w.w;
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int s = 0; s < kGroupSlabs; s++) {
+            if (s < nslab) {
+              const unsigned char* gp = sbase + s * kSlotBytes + goffs;
+#pragma unroll
+              for (int r = 0; r < 8; r++) {
+                const float2 w = *reinterpret_cast<const float2*>(gp + r * kRowPitch);
+                G[s][2 * r] = w.x; G[s][2 * r + 1] = w.y;
+              }
+            }
+          }
+        }
+        const float4* coef = reinterpret_cast<const float4*>(sbase + kCoefOff);
+        const float4* o = reinterpret_cast<const float4*>(smem_raw + d0.y + q * 64);
+        const int ostep = d0.z >> 4;
+        float2* a = mine + d0.w * 32;
+        const int astep = d1.x * 32;
+        switch (nslab) {
+          case 1: band_loop<1>(G, coef, cnt, o, ostep, a, astep); break;
+          case 2: band_loop<2>(G, coef, cnt, o, ostep, a, astep); break;
+          case 3: band_loop<3>(G, coef, cnt, o, ostep, a, astep); break;
+          default: band_loop<4>(G, coef, cnt, o, ostep, a, astep); break;
+        }
+        if (d0.x & 0x10000) {  // last group of the pair-tile: the warp's partial rows go to the CTA's accumulators
+          const int rows = (d0.x >> 24) & 0xff;
+          float* dst = acc_f + d1.y + 2 * lane;
+          for (int j = 0; j < rows; j++) {
+            const float2 v = mine[j * 32];
+            mine[j * 32] = make_float2(0.f, 0.f);
+            atomicAdd(dst + j * d1.z, v.x);
+            atomicAdd(dst + j * d1.z + 1, v.y);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[st]);  // the stage (slabs, coefficients, descriptors) is free again
+    }
+    if (!ok && lane == 0) *A.status = 1;
+  }
+
+  __syncthreads();
+  if (A.do_x) flush_rows(acc_f, A.xg, xgoff, A.xoff, A.nx, A.x_atomic != 0);
+  if (A.do_y) flush_rows(acc_f, A.yg, ygoff, A.yoff, A.ny, A.y_atomic != 0);
+}
+
+}  // namespace
+
+// Returns -1 when the call does not qualify (the caller then takes the kernel of cg_bwd.cu).
+int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s) {
+  static const char* fn = "SO3vec_addCGproduct_back";
+  if (!c.vec_ok) return -1;
+  if (c.x.empty() || c.y.empty() || c.r.empty()) return -1;
+  int lmax = 0;
+  for (const auto& p : c.x) { if (p.n % 32 || p.n > 32768) return -1; lmax = std::max(lmax, p.l); }
+  for (const auto& p : c.y) { if (p.n % 32 || p.n > 32768) return -1; lmax = std::max(lmax, p.l); }
+  for (const auto& p : c.r) if (p.l > 16) return -1;
+  if (lmax > 8) return -1;
+  if (c.cg.ncells > 0x7fffffffLL) return -1;
+  int* status = async_status_word(kStatusBwdPair);
+  if (!status) return -1;
+  const int J = 2 * lmax + 1;
+
+  PairArgs a;
+  int off = 0;
+  for (size_t i = 0; i < c.x.size(); i++) {
+    a.x[i] = c.x[i];
+    if (!c.xg.empty()) a.xg[i] = c.xg[i];
+    a.xoff[i] = off;
+    off += 2 * (2 * c.x[i].l + 1) * c.x[i].n;
+  }
+  for (size_t i = 0; i < c.y.size(); i++) {
+    a.y[i] = c.y[i];
+    if (!c.yg.empty()) a.yg[i] = c.yg[i];
+    a.yoff[i] = off;
+    off += 2 * (2 * c.y[i].l + 1) * c.y[i].n;
+  }
+  for (size_t i = 0; i < c.r.size(); i++) a.g[i] = c.r[i];
+  a.nx = (int)c.x.size();
+  a.ny = (int)c.y.size();
+  a.ng = (int)c.r.size();
+  a.cell_floats = off;
+  const size_t fixed = ((size_t)kHeaderBytes + (size_t)8 * off + (size_t)kConsumers * J * 256 + 127) & ~(size_t)127;
+  int ns = kMaxStages;
+  while (ns >= 2 && fixed + (size_t)ns * kStageBytes > 227 * 1024) ns--;
+  if (ns < 2) return -1;
+  a.nstages = ns;
+  const size_t smem = fixed + (size_t)ns * kStageBytes;
+
+  std::vector<int> key = {10 /*family*/, (int)c.x.size(), (int)c.y.size(), (int)c.r.size()};
+  for (const auto& p : c.x) { key.push_back(p.l); key.push_back(p.n); }
+  for (const auto& p : c.y) { key.push_back(p.l); key.push_back(p.n); }
+  for (const auto& p : c.r) key.push_back(p.l);
+  const auto xs = sig_of(c.x), ys = sig_of(c.y), rs = sig_of(c.r);
+  const int *xoff = a.xoff, *yoff = a.yoff;
+  DevicePlan* plan = get_plan(key, [&](DevicePlan& p) {
+    build_schedule(xs, ys, rs, false, true, &p.sched);
+    // triples of each (xi, yi) pair, in schedule order (l ascending)
+    std::map<std::pair<int, int>, std::vector<const Triple*>> pairs;
+    for (const Triple& t : p.sched.triples) pairs[{t.xi, t.yi}].push_back(&t);
+    std::vector<float>& quads = p.h_floats;
+    for (const auto& kv : pairs) {
+      const auto& ts = kv.second;
+      const int xi = kv.first.first, yi = kv.first.second;
+      const int l1 = xs[xi].l, l2 = ys[yi].l, n1 = xs[xi].n, n2 = ys[yi].n;
+      int lm = 0;
+      for (const Triple* t : ts) lm = std::max<int>(lm, t->l);
+      for (int a0 = 0; a0 < n1; a0 += 32)
+        for (int b0 = 0; b0 < n2; b0 += 32) {
+          const size_t first_rec = p.h_items.size();
+          for (int m = -lm; m <= lm; m++) {
+            const int lo = std::max(-l1, m - l2), hi = std::min(l1, m + l2);
+            const int cnt = hi - lo + 1, jlo = lo + l1, j2hi = m - lo + l2;
+            std::vector<const Triple*> act;
+            for (const Triple* t : ts)
+              if (t->l >= std::abs(m)) act.push_back(t);
+            for (size_t c0 = 0; c0 < act.size(); c0 += kGroupSlabs) {
+              const int nslab = (int)std::min<size_t>(kGroupSlabs, act.size() - c0);
+              int sw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+              for (int sidx = 0; sidx < nslab; sidx++) {
+                const Triple* t = act[c0 + sidx];
+                sw[2 * sidx] = t->ri | ((m + t->l) << 8);
+                sw[2 * sidx + 1] = t->offs + a0 * n2 + b0;
+              }
+              const int head = nslab | (cnt << 8);
+              // xg warps: y rows downwards from m2 = m - lo, accumulator rows upwards from m1 = lo
+              p.h_items.push_back(make_int4(head | ((2 * l1 + 1) << 24), kHeaderBytes + 4 * (yoff[yi] + 2 * b0 + 2 * n2 * j2hi),
+                                            -8 * n2, jlo));
+              p.h_items.push_back(make_int4(1, xoff[xi] + 2 * a0, 2 * n1, 0));
+              // yg warps: x rows upwards from m1 = lo, accumulator rows downwards from m2 = m - lo
+              p.h_items.push_back(make_int4(head | ((2 * l2 + 1) << 24), kHeaderBytes + 4 * (xoff[xi] + 2 * a0 + 2 * n1 * jlo),
+                                            8 * n1, j2hi));
+              p.h_items.push_back(make_int4(-1, yoff[yi] + 2 * b0, 2 * n2, 0));
+              p.h_items.push_back(make_int4(head | (n2 << 16), (int)(quads.size() / 4), sw[0], sw[1]));
+              p.h_items.push_back(make_int4(sw[2], sw[3], sw[4], sw[5]));
+              p.h_items.push_back(make_int4(sw[6], sw[7], 0, 0));
+              for (int m1 = lo; m1 <= hi; m1++)
+                for (int sidx = 0; sidx < kGroupSlabs; sidx++) {
+                  float cf = 0.f;
+                  if (sidx < nslab) {
+                    const Triple* t = act[c0 + sidx];
+                    // band order of the schedule's table: rows m ascending, m1 ascending within a row
+                    int pos = t->coff;
+                    for (int mm = -t->l; mm < m; mm++)
+                      pos += std::min<int>(l1, mm + l2) - std::max<int>(-l1, mm - l2) + 1;
+                    cf = p.sched.coeffs[pos + (m1 - lo)];
+                  }
+                  quads.push_back(cf);
+                }
+            }
+          }
+          if (p.h_items.size() > first_rec) {  // mark the last group of the pair-tile in both descriptors
+            p.h_items[p.h_items.size() - kRec].x |= 0x10000;
+            p.h_items[p.h_items.size() - kRec + 2].x |= 0x10000;
+          }
+        }
+    }
+  });
+  if (!plan) return GELIB_CUDA_ERROR;
+  if (plan->nitems == 0 || c.cg.ncells == 0) return GELIB_OK;
+
+  a.cg = c.cg;
+  a.recs = plan->items;
+  a.ngroups = plan->nitems / kRec;
+  a.coef = reinterpret_cast<const float4*>(plan->floats);
+  a.offs_extra = c.offs_extra;
+  a.do_x = c.xg.empty() ? 0 : 1;
+  a.do_y = c.yg.empty() ? 0 : 1;
+  a.x_atomic = c.xg_bcast ? 1 : 0;
+  a.y_atomic = c.yg_bcast ? 1 : 0;
+  a.skip_group = inject_timeout() ? 0 : -1;
+  a.status = status;
+
+  cudaError_t e = cudaFuncSetAttribute(cg_bwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e == cudaSuccess) {
+    cg_bwd_pair_kernel<<<(unsigned)c.cg.ncells, kThreads, smem, s>>>(a, J);
+    e = cudaGetLastError();
+  }
+  if (e != cudaSuccess) return check_cuda(e, fn, "pair backward kernel launch");
+  count_launch();
+  return GELIB_OK;
+}
+
+}  // namespace gelib_b200

@@ -449,21 +449,6 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_tc_kernel(const __grid_con
 
 namespace {
 
-int* status_word() {  // one host-mapped word for the process; kernels of any device can set it
-  static int* w = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    if (cudaHostAlloc(&p, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess) {
-      w = static_cast<int*>(p);
-      *w = 0;
-    } else {
-      cudaGetLastError();
-    }
-  });
-  return w;
-}
-
 inline int round_up(int v, int q) { return (v + q - 1) / q * q; }
 
 }  // namespace
@@ -471,19 +456,14 @@ inline int round_up(int v, int q) { return (v + q - 1) / q * q; }
 // Returns -1 when the call does not qualify (the caller then takes the SIMT kernels).
 int launch_cg_bwd_tc(const VecCall& c, cudaStream_t s) {
   static const char* fn = "SO3vec_addCGproduct_back";
-  if (!c.vec_ok || c.xg.empty() || c.yg.empty()) return -1;
+  if (!c.vec_ok || !c.in_vec_ok || c.xg.empty() || c.yg.empty()) return -1;
   if (c.x.size() > 15 || c.y.size() > 15 || c.r.size() > 15) return -1;
   for (const auto& p : c.x) if (p.n % 32 || p.l > 7 || p.n > 32768) return -1;
   for (const auto& p : c.y) if (p.n % 32 || p.l > 7 || p.n > 32768) return -1;
   for (const auto& p : c.r) if (p.l > 127) return -1;
   if (!device_has_tcgen05()) return -1;
-  int* status = status_word();
+  int* status = async_status_word(kStatusBwdTc);
   if (!status) return -1;
-  if (*status != 0) {
-    *status = 0;
-    set_error(std::string(fn) + ": a tensor-core backward kernel gave up waiting on an mbarrier; its gradients are incomplete.");
-    return GELIB_CUDA_ERROR;
-  }
 
   // Each CTA works on one product and holds only that product's tables and gradient rows: offsets of the y tables /
   // x gradient rows (P) and of the x tables / y gradient rows (Q) both start at 0.

@@ -221,14 +221,14 @@ int launch_cg_fwd(const VecCall& c, cudaStream_t s) {
   // Calls that qualify (channel counts that are multiples of 32, output overwritten) and have at least 512 slabs
   // (rows of 32 x 32 channel tiles) per cell go to the tensor-core kernel of cg_fwd_tc.cu: with fewer its fixed
   // cost per cell (staging the y tables, tensor-memory allocation) outweighs its cheaper slabs.
-  // GELIB_B200_FWD=simt keeps everything on this file's kernel, "tcgen05" sends everything that qualifies there,
-  // "tcgen05!" also refuses calls that do not qualify (tests use it to be sure which kernel ran).
-  const char* which = getenv("GELIB_B200_FWD");
-  const std::string mode = which ? which : "auto";
-  if (mode != "simt") {
-    const int rc = launch_cg_fwd_tc(c, s, mode == "auto" ? 512 : 0);
+  // Option "fwd" (initially GELIB_B200_FWD): "simt" keeps everything on this file's kernel, "tcgen05" sends
+  // everything that qualifies there, "tcgen05!" also refuses calls that do not qualify (tests use it to be sure which
+  // kernel ran).
+  const int mode = fwd_mode();
+  if (mode != kFwdSimt) {
+    const int rc = launch_cg_fwd_tc(c, s, mode == kFwdAuto ? 512 : 0);
     if (rc != -1) return rc;
-    if (mode == "tcgen05!") return fail(GELIB_INVALID, fn, "the call does not qualify for the tcgen05 kernel");
+    if (mode == kFwdTcStrict) return fail(GELIB_INVALID, fn, "the call does not qualify for the tcgen05 kernel");
   }
   // ---- choose the lane layout: least padded work on the dominant channel counts, then the widest tile
   int n1 = 1, n2 = 1;

@@ -294,21 +294,6 @@ __global__ void __launch_bounds__(kThreads, 1) cg_fwd_tc_kernel(const __grid_con
 
 namespace {
 
-int* fwd_status_word() {  // one host-mapped word for the process
-  static int* w = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    if (cudaHostAlloc(&p, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess) {
-      w = static_cast<int*>(p);
-      *w = 0;
-    } else {
-      cudaGetLastError();
-    }
-  });
-  return w;
-}
-
 inline int round_up(int v, int q) { return (v + q - 1) / q * q; }
 
 }  // namespace
@@ -317,7 +302,7 @@ inline int round_up(int v, int q) { return (v + q - 1) / q * q; }
 // SIMT kernel).
 int launch_cg_fwd_tc(const VecCall& c, cudaStream_t s, int min_slabs) {
   static const char* fn = "SO3vec_addCGproduct";
-  if (!c.vec_ok || !(c.flags & GELIB_OVERWRITE) || c.r_bcast) return -1;
+  if (!c.vec_ok || !c.in_vec_ok || !(c.flags & GELIB_OVERWRITE) || c.r_bcast) return -1;
   if (c.x.size() > 15 || c.y.size() > 15 || c.r.size() > 15) return -1;
   for (const auto& p : c.x) if (p.n % 32 || p.l > 7 || p.n > 32768) return -1;
   for (const auto& p : c.y) if (p.n % 32 || p.l > 7 || p.n > 32768) return -1;
@@ -331,13 +316,8 @@ int launch_cg_fwd_tc(const VecCall& c, cudaStream_t s, int min_slabs) {
     if (slabs < min_slabs) return -1;
   }
   if (!device_has_tcgen05()) return -1;
-  int* status = fwd_status_word();
+  int* status = async_status_word(kStatusFwdTc);
   if (!status) return -1;
-  if (*status != 0) {
-    *status = 0;
-    set_error(std::string(fn) + ": a tensor-core forward kernel gave up waiting on an mbarrier; its output is incomplete.");
-    return GELIB_CUDA_ERROR;
-  }
 
   FwdTcArgs a;
   int bt = 0, xf = 0;
@@ -414,9 +394,8 @@ int launch_cg_fwd_tc(const VecCall& c, cudaStream_t s, int min_slabs) {
   a.groups = plan->items;
   a.ngroups = plan->nitems / kRec;
   a.offs_extra = c.offs_extra;
-  // GELIB_B200_INJECT_TIMEOUT=1 (tests only): exercise the bounded waits and the status word without any fault
-  const char* inject = getenv("GELIB_B200_INJECT_TIMEOUT");
-  a.drop_commit = inject && atoi(inject) != 0;
+  // option "inject_timeout" (tests only): exercise the bounded waits and the status word without any fault
+  a.drop_commit = inject_timeout();
   a.status = status;  // unified addressing: the host pointer of mapped memory is valid on the device
   cudaError_t e = cudaFuncSetAttribute(cg_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e == cudaSuccess) {

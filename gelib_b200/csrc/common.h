@@ -95,9 +95,11 @@ struct DevicePlan {
   float* coeffs = nullptr;
   int4* items = nullptr;   // kernel-specific work list
   int* jobs = nullptr;     // job j covers items [jobs[j], jobs[j+1])
+  float* floats = nullptr; // kernel-specific float table (16-byte aligned)
   int ntriples = 0, nitems = 0, njobs = 0;
   std::vector<int4> h_items;
   std::vector<int> h_jobs;
+  std::vector<float> h_floats;
   Schedule sched;
 };
 

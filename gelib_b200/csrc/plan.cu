@@ -4,6 +4,9 @@
 // them to "the" GPU on first use (SO3/SO3CGbank.hpp:33-49, single device only).  Here a plan is
 // keyed by (device, kernel family, tiling, part signature), built once under a mutex and kept in
 // device memory for the life of the process, so any number of devices can be used from one process.
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
 #include <map>
 #include <mutex>
 
@@ -29,6 +32,113 @@ bool upload(const std::vector<T>& h, T** d) {
   return cudaMemcpy(*d, h.data(), h.size() * sizeof(T), cudaMemcpyHostToDevice) == cudaSuccess;
 }
 }  // namespace
+
+// ---- options ------------------------------------------------------------------------------------------------
+
+namespace {
+struct Options {
+  std::atomic<int> fwd{kFwdAuto}, bwd{kBwdAuto}, inject{0};
+};
+int parse_fwd(const char* v) {
+  if (!v || !*v || !strcmp(v, "auto")) return kFwdAuto;
+  if (!strcmp(v, "simt")) return kFwdSimt;
+  if (!strcmp(v, "tcgen05")) return kFwdTc;
+  if (!strcmp(v, "tcgen05!")) return kFwdTcStrict;
+  return -1;
+}
+int parse_bwd(const char* v) {
+  if (!v || !*v || !strcmp(v, "auto")) return kBwdAuto;
+  if (!strcmp(v, "simt")) return kBwdSimt;
+  if (!strcmp(v, "pair")) return kBwdPair;
+  if (!strcmp(v, "pair!")) return kBwdPairStrict;
+  if (!strcmp(v, "tcgen05")) return kBwdTc;
+  if (!strcmp(v, "tcgen05!")) return kBwdTcStrict;
+  return -1;
+}
+Options& options() {
+  static Options o;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    const int f = parse_fwd(getenv("GELIB_B200_FWD")), b = parse_bwd(getenv("GELIB_B200_BWD"));
+    o.fwd = f < 0 ? kFwdAuto : f;
+    o.bwd = b < 0 ? kBwdAuto : b;
+    const char* inj = getenv("GELIB_B200_INJECT_TIMEOUT");
+    o.inject = inj && atoi(inj) != 0;
+  });
+  return o;
+}
+}  // namespace
+
+int fwd_mode() { return options().fwd.load(std::memory_order_relaxed); }
+int bwd_mode() { return options().bwd.load(std::memory_order_relaxed); }
+bool inject_timeout() { return options().inject.load(std::memory_order_relaxed) != 0; }
+
+int set_option(const char* name, const char* value) {
+  if (!name) return GELIB_INVALID;
+  Options& o = options();
+  if (!strcmp(name, "fwd")) {
+    const int v = parse_fwd(value);
+    if (v < 0) return GELIB_INVALID;
+    o.fwd = v;
+    return GELIB_OK;
+  }
+  if (!strcmp(name, "bwd")) {
+    const int v = parse_bwd(value);
+    if (v < 0) return GELIB_INVALID;
+    o.bwd = v;
+    return GELIB_OK;
+  }
+  if (!strcmp(name, "inject_timeout")) {
+    o.inject = value && atoi(value) != 0;
+    return GELIB_OK;
+  }
+  return GELIB_INVALID;
+}
+
+// ---- status words of kernels with bounded waits --------------------------------------------------------------
+
+namespace {
+int* status_words() {
+  static int* w = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, kStatusCount * sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess) {
+      w = static_cast<int*>(p);
+      for (int i = 0; i < kStatusCount; i++) w[i] = 0;
+    } else {
+      cudaGetLastError();
+    }
+  });
+  return w;
+}
+std::atomic<bool> g_status_in_use{false};
+}  // namespace
+
+int* async_status_word(int which) {
+  int* w = status_words();
+  if (!w) return nullptr;
+  g_status_in_use.store(true, std::memory_order_relaxed);
+  return w + which;
+}
+
+int poll_async_status(const char* fn) {
+  if (!g_status_in_use.load(std::memory_order_relaxed)) return GELIB_OK;  // no kernel with bounded waits has run yet
+  volatile int* w = status_words();
+  static const char* what[kStatusCount] = {"the tensor-core forward kernel (cg_fwd_tc_kernel); its output is incomplete",
+                                           "the tensor-core backward kernel (cg_bwd_tc_kernel); its gradients are incomplete",
+                                           "the backward kernel (cg_bwd_pair_kernel); its gradients are incomplete"};
+  std::string msg;
+  for (int i = 0; i < kStatusCount; i++)
+    if (w[i] != 0) {
+      w[i] = 0;
+      if (!msg.empty()) msg += "; ";
+      msg += what[i];
+    }
+  if (msg.empty()) return GELIB_OK;
+  set_error(std::string(fn) + ": an earlier launch gave up waiting on an mbarrier in " + msg + ".");
+  return GELIB_CUDA_ERROR;
+}
 
 bool device_has_tcgen05() {
   static std::mutex mu;
@@ -68,13 +178,15 @@ DevicePlan* get_plan(const std::vector<int>& key, const std::function<void(Devic
   p->nitems = (int)p->h_items.size();
   p->njobs = p->h_jobs.empty() ? 0 : (int)p->h_jobs.size() - 1;
   bool ok = upload(p->sched.triples, &p->triples) && upload(p->sched.coeffs, &p->coeffs) &&
-            upload(p->h_items, &p->items) && upload(p->h_jobs, &p->jobs);
+            upload(p->h_items, &p->items) && upload(p->h_jobs, &p->jobs) &&
+            upload(p->h_floats, &p->floats);
   if (!ok) {
     set_error(std::string("CUDA error while uploading a product plan: ") + cudaGetErrorString(cudaGetLastError()));
     cudaFree(p->triples);
     cudaFree(p->coeffs);
     cudaFree(p->items);
     cudaFree(p->jobs);
+    cudaFree(p->floats);
     delete p;
     return nullptr;
   }

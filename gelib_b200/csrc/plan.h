@@ -18,7 +18,8 @@ struct VecCall {
   bool r_bcast = false;  // an output tensor is broadcast over cells: results must be summed (atomics)
   bool xg_bcast = false, yg_bcast = false;
   bool dense_channels = true;  // every tensor has channel stride 2 floats
-  bool vec_ok = true;          // 16-byte alignment of bases/strides/offsets holds for float4 access
+  bool vec_ok = true;          // 16-byte alignment of bases/strides/offsets of r (g) holds, offsets and n2 even
+  bool in_vec_ok = true;       // 16-byte alignment of every x, y, xg, yg part (float4 access to the small operands)
 };
 
 std::vector<PartSig> sig_of(const std::vector<PartView>& v);
@@ -32,6 +33,7 @@ int launch_cg_fwd(const VecCall& c, cudaStream_t s);
 int launch_cg_fwd_tc(const VecCall& c, cudaStream_t s, int min_slabs);  // tcgen05 kernel; -1 when the call does not qualify or has fewer slabs per cell
 int launch_cg_bwd(const VecCall& c, cudaStream_t s);
 int launch_cg_bwd_tc(const VecCall& c, cudaStream_t s);  // tcgen05 kernel; -1 when the call does not qualify
+int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s);  // uncoupled-gradient kernel; -1 when the call does not qualify
 int launch_cg_narrow_bwd(const VecCall& c, cudaStream_t s);
 int launch_cg_narrow_fwd(const VecCall& c, cudaStream_t s);  // x with at most 4 channels; -1 when the call does not qualify
 int launch_cg_strided(const VecCall& c, int mode, cudaStream_t s);  // mode 0 fwd, 1 back0, 2 back1
@@ -43,6 +45,22 @@ int launch_diag_bwd_fast(const VecCall& c, cudaStream_t s);  // -1 when the call
 void build_diag_items(DevicePlan& p, const std::vector<PartSig>& xs, const std::vector<PartSig>& ys,
                       const std::vector<PartSig>& rs, int* max_nl);
 int launch_spharm(const std::vector<PartView>& r, const PartView& x, const CellGrid& cg, int flags, cudaStream_t s);
+
+// Kernel selection and debug switches.  Initial values come from the environment (GELIB_B200_FWD, GELIB_B200_BWD,
+// GELIB_B200_INJECT_TIMEOUT), read once at first use; gelib_set_option changes them afterwards.  Launch paths read
+// one atomic integer.
+enum FwdMode { kFwdAuto = 0, kFwdSimt, kFwdTc, kFwdTcStrict };
+enum BwdMode { kBwdAuto = 0, kBwdSimt, kBwdPair, kBwdPairStrict, kBwdTc, kBwdTcStrict };
+int fwd_mode();
+int bwd_mode();
+bool inject_timeout();  // tests only: make one bounded device wait run out (no fault is involved)
+int set_option(const char* name, const char* value);  // GELIB_OK or GELIB_INVALID
+
+// Host-mapped status words that kernels with bounded waits set when a wait ran out.  One word per kernel family;
+// every C-ABI product call and gelib_async_status() poll and clear them.
+enum { kStatusFwdTc = 0, kStatusBwdTc = 1, kStatusBwdPair = 2, kStatusCount = 3 };
+int* async_status_word(int which);        // nullptr when the mapped allocation failed
+int poll_async_status(const char* fn);    // GELIB_OK, or GELIB_CUDA_ERROR with the message set (words cleared)
 
 bool device_has_tcgen05();  // compute capability 10.x on the current device (cached per device)
 long long launch_count();

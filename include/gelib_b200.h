@@ -152,6 +152,22 @@ int gelib_SO3vec_addSPharm(int nr, const gelib_tensor5* r, const gelib_tensor5* 
 /* Number of kernels this library has launched in the calling process (all threads, all devices). */
 long long gelib_kernel_launch_count(void);
 
+/* Kernel selection and test switches.  The reference chooses between its kernels inside the launcher
+ * (cuda/SO3part_addCGproduct.cu:226-262: tiled or not, coefficients preloaded or not) with no way to steer it;
+ * here the choice can be pinned.  name "fwd": "auto" | "simt" | "tcgen05" | "tcgen05!";  name "bwd": "auto" |
+ * "simt" | "pair" | "pair!" | "tcgen05" | "tcgen05!" (a trailing "!" refuses calls the named kernel cannot take
+ * instead of falling back);  name "inject_timeout": "0" | "1" (tests: one bounded device wait is made to run out).
+ * Initial values: the environment variables GELIB_B200_FWD, GELIB_B200_BWD, GELIB_B200_INJECT_TIMEOUT, read once
+ * at first use.  Returns GELIB_OK or GELIB_INVALID. */
+int gelib_set_option(const char* name, const char* value);
+
+/* The kernels that wait on mbarriers bound every wait; one that gives up records it in host-mapped memory and
+ * returns with incomplete output.  Every product entry point above checks that record first and returns
+ * GELIB_CUDA_ERROR for an earlier launch's failure; a caller that wants to know before its next product call
+ * synchronises the stream and calls this (GELIB_OK, or GELIB_CUDA_ERROR with the kernel named in
+ * gelib_last_error(); the record is cleared).  The reference has no counterpart: its kernels never wait. */
+int gelib_async_status(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -23,6 +23,20 @@ def G():
     return gelib_b200
 
 
+@pytest.fixture
+def opt(G):
+    """Pins kernel choices / test switches of the library for one test and restores the defaults afterwards."""
+    touched = []
+
+    def set_(name, value):
+        touched.append(name)
+        G._lib.set_option(name, value)
+
+    yield set_
+    for name in touched:
+        G._lib.set_option(name, "0" if name == "inject_timeout" else "auto")
+
+
 def dev(t):
     return t.cuda()
 
@@ -209,6 +223,7 @@ VEC_CASES = [
     (2, {l: 8 for l in range(7)}, {l: 8 for l in range(7)}, 6, TOL_BIG),
     (9, {l: 1 for l in range(7)}, {l: 16 for l in range(7)}, 6, TOL_BIG),
     (2, {1: 64}, {2: 64}, -1, TOL),
+    (2, {3: 64}, {4: 64}, -1, TOL_BIG),   # the SO3part benchmark configuration l1=3 x l2=4 -> l=1..7 as one vector call
 ]
 
 
@@ -288,10 +303,16 @@ TC_CASES = [
 ]
 
 
-@pytest.mark.parametrize("B,tau_x,tau_y,maxl,tol", TC_CASES)
+@pytest.mark.parametrize("B,tau_x,tau_y,maxl,tol", TC_CASES + [
+    (3, {l: 32 for l in range(9)}, {l: 32 for l in range(9)}, 8, TOL_BIG),   # 17 accumulator rows, groups of 5..9 l split in two
+    (2, {2: 32, 5: 64}, {0: 64, 4: 32, 6: 32}, 5, TOL_BIG),                 # gaps in l, truncated output
+])
 @pytest.mark.parametrize("bcast_y", [False, True])
-def test_vec_backward_tcgen05(G, oracle, monkeypatch, B, tau_x, tau_y, maxl, tol, bcast_y):
-    monkeypatch.setenv("GELIB_B200_BWD", "tcgen05!")  # fail instead of falling back to the SIMT kernel
+@pytest.mark.parametrize("kernel", ["pair!", "tcgen05!", "simt"])
+def test_vec_backward_named_kernel(G, oracle, opt, B, tau_x, tau_y, maxl, tol, bcast_y, kernel):
+    if kernel == "tcgen05!" and max(list(tau_x) + list(tau_y)) > 7:
+        pytest.skip("the tcgen05 backward covers l <= 7")
+    opt("bwd", kernel)  # "!": fail instead of falling back to another kernel
     x, y = _vec_inputs(tau_x, tau_y, B, 90)
     if bcast_y:
         y = {l: t[:1].contiguous() for l, t in y.items()}
@@ -318,8 +339,9 @@ def test_vec_backward_tcgen05(G, oracle, monkeypatch, B, tau_x, tau_y, maxl, tol
 
 
 @pytest.mark.parametrize("B,tau_x,tau_y,maxl,tol", TC_CASES)
-def test_vec_forward_tcgen05(G, oracle, monkeypatch, B, tau_x, tau_y, maxl, tol):
-    monkeypatch.setenv("GELIB_B200_FWD", "tcgen05!")  # fail instead of falling back to the SIMT kernel
+@pytest.mark.parametrize("kernel", ["tcgen05!", "simt", "auto"])
+def test_vec_forward_named_kernel(G, oracle, opt, B, tau_x, tau_y, maxl, tol, kernel):
+    opt("fwd", kernel)  # "tcgen05!": fail instead of falling back to the SIMT kernel
     x, y = _vec_inputs(tau_x, tau_y, B, 60)
     tau_r = oracle.cg_type(tau_x, tau_y, maxl, False)
     want = {l: np.zeros((B, 2 * l + 1, n), np.complex64) for l, n in tau_r.items()}
@@ -336,11 +358,11 @@ def test_vec_forward_tcgen05(G, oracle, monkeypatch, B, tau_x, tau_y, maxl, tol)
         assert rel_err(p, w) < TOL, l
 
 
-def test_tcgen05_wait_that_runs_out_is_reported(G, oracle, monkeypatch):
+def test_tcgen05_wait_that_runs_out_is_reported(G, oracle, opt):
     """The kernel's mbarrier waits are bounded: when the completion never arrives (injected on the host: the MMAs
     are issued but not committed) the kernel gives up within a fraction of a second, frees its tensor memory and
-    returns; the next call reports it, and the one after that works again."""
-    monkeypatch.setenv("GELIB_B200_FWD", "tcgen05!")
+    returns; the next product call of any kind reports it, and the one after that works again."""
+    opt("fwd", "tcgen05!")
     tau = {l: 32 for l in range(3)}
     x, y = _vec_inputs(tau, tau, 2, 77)
     tau_r = oracle.cg_type(tau, tau, 2, False)
@@ -348,22 +370,59 @@ def test_tcgen05_wait_that_runs_out_is_reported(G, oracle, monkeypatch):
     yv = G.backend.SO3vec.view([dev(t) for t in y.values()])
     rparts = [torch.zeros(2, 2 * l + 1, n, dtype=torch.complex64, device="cuda") for l, n in tau_r.items()]
     rv = G.backend.SO3vec.view(rparts)
-    monkeypatch.setenv("GELIB_B200_INJECT_TIMEOUT", "1")
+    opt("inject_timeout", "1")
     rv.addCGproduct(xv, yv, overwrite=True)   # launches; its waits run out on the device
     torch.cuda.synchronize()                  # the context stays usable
-    monkeypatch.delenv("GELIB_B200_INJECT_TIMEOUT")
+    opt("inject_timeout", "0")
+    small = torch.zeros(2, 3, 4, dtype=torch.complex64, device="cuda")
+    sx = dev(crandn(1, 2, 3, 2))
     with pytest.raises(Exception, match="gave up waiting"):
-        rv.addCGproduct(xv, yv, overwrite=True)
+        view(G, small).add_DiagCGproduct(view(G, sx), view(G, sx))   # a call that takes another kernel reports it
+    assert small.abs().max() == 0
     rv.addCGproduct(xv, yv, overwrite=True)   # the status was cleared: this one computes
     torch.cuda.synchronize()
+    G._lib.async_status()
     want = {l: np.zeros((2, 2 * l + 1, n), np.complex64) for l, n in tau_r.items()}
     oracle.vec_cg(want, {l: np_c(t) for l, t in x.items()}, {l: np_c(t) for l, t in y.items()}, False)
     for p, (l, w) in zip(rparts, want.items()):
         assert rel_err(p, w) < TOL, l
 
 
-def test_tcgen05_refuses_what_it_cannot_do(G, monkeypatch):
-    monkeypatch.setenv("GELIB_B200_BWD", "tcgen05!")
+def test_pair_backward_wait_that_runs_out_is_reported(G, oracle, opt):
+    """Same for the default backward kernel: the producer warp leaves out one group's copies (a host-side switch), the
+    consumers' bounded waits run out, the kernel returns, gelib_async_status() names the kernel, the next call works."""
+    opt("bwd", "pair!")
+    tau = {l: 32 for l in range(3)}
+    x, y = _vec_inputs(tau, tau, 2, 78)
+    tau_r = oracle.cg_type(tau, tau, 2, False)
+    g = {l: crandn(500 + l, 2, 2 * l + 1, n) for l, n in tau_r.items()}
+    xv = G.backend.SO3vec.view([dev(t) for t in x.values()])
+    yv = G.backend.SO3vec.view([dev(t) for t in y.values()])
+    gv = G.backend.SO3vec.view([dev(t) for t in g.values()])
+
+    def run():
+        xg = [torch.zeros(t.shape, dtype=torch.complex64, device="cuda") for t in x.values()]
+        yg = [torch.zeros(t.shape, dtype=torch.complex64, device="cuda") for t in y.values()]
+        G.backend.SO3vec.addCGproduct_back01(G.backend.SO3vec.view(xg), G.backend.SO3vec.view(yg), gv, xv, yv)
+        torch.cuda.synchronize()
+        return xg, yg
+
+    opt("inject_timeout", "1")
+    run()
+    opt("inject_timeout", "0")
+    with pytest.raises(Exception, match="cg_bwd_pair_kernel"):
+        G._lib.async_status()
+    xg, yg = run()
+    G._lib.async_status()
+    gn = {l: np_c(t) for l, t in g.items()}
+    xg_w = {l: np.zeros(t.shape, np.complex64) for l, t in x.items()}
+    oracle.vec_cg_back0(xg_w, gn, {l: np_c(t) for l, t in y.items()}, False)
+    for p, w in zip(xg, xg_w.values()):
+        assert rel_err(p, w) < TOL_BIG
+
+
+def test_tcgen05_refuses_what_it_cannot_do(G, opt):
+    opt("bwd", "tcgen05!")
     tau = {0: 8, 1: 8}
     x, y = _vec_inputs(tau, tau, 2, 5)
     xv = G.backend.SO3vec.view([dev(t) for t in x.values()])
@@ -374,6 +433,124 @@ def test_tcgen05_refuses_what_it_cannot_do(G, monkeypatch):
     yg = [torch.zeros(t.shape, dtype=torch.complex64, device="cuda") for t in y.values()]
     with pytest.raises(Exception):
         G.backend.SO3vec.addCGproduct_back01(G.backend.SO3vec.view(xg), G.backend.SO3vec.view(yg), gv, xv, yv)
+    opt("bwd", "pair!")
+    with pytest.raises(Exception):
+        G.backend.SO3vec.addCGproduct_back01(G.backend.SO3vec.view(xg), G.backend.SO3vec.view(yg), gv, xv, yv)
+
+
+
+# ---- the benchmark configurations' own layouts ----------------------------------------------------------------
+
+def test_diag_vector_maxl8_128_channels(G, oracle):
+    """DiagCGproduct of SO3vecs with parts l = 0..8, 128 channels each, truncated at 8 (369 triples): the layout of the
+    diagonal benchmark configuration, which takes the one-cell-per-CTA kernels with multi-chunk staging."""
+    B, tau = 2, {l: 128 for l in range(9)}
+    x, y = _vec_inputs(tau, tau, B, 20)
+    tau_r = oracle.cg_type(tau, tau, 8, True)
+    assert list(tau_r.values()) == [1152, 3072, 4608, 5760, 6528, 6912, 6912, 6528, 5760]
+    xn, yn = {l: np_c(t) for l, t in x.items()}, {l: np_c(t) for l, t in y.items()}
+    want = {l: np.zeros((B, 2 * l + 1, n), np.complex64) for l, n in tau_r.items()}
+    oracle.vec_cg(want, xn, yn, True)
+    xv = G.backend.SO3vec.view([dev(t) for t in x.values()])
+    yv = G.backend.SO3vec.view([dev(t) for t in y.values()])
+    rparts = [torch.full((B, 2 * l + 1, n), 7.0 + 3.0j, dtype=torch.complex64, device="cuda") for l, n in tau_r.items()]
+    G.backend.SO3vec.view(rparts).addDiagCGproduct(xv, yv, overwrite=True)
+    for p, (l, w) in zip(rparts, want.items()):
+        assert rel_err(p, w) < TOL_BIG, l
+    racc = [torch.ones_like(p) for p in rparts]
+    G.backend.SO3vec.view(racc).addDiagCGproduct(xv, yv)
+    for p, (l, w) in zip(racc, want.items()):
+        assert rel_err(p - 1, w) < TOL_BIG, l
+    g = {l: crandn(300 + l, B, 2 * l + 1, n) for l, n in tau_r.items()}
+    gn = {l: np_c(t) for l, t in g.items()}
+    xg_w = {l: np.zeros(t.shape, np.complex64) for l, t in x.items()}
+    yg_w = {l: np.zeros(t.shape, np.complex64) for l, t in y.items()}
+    oracle.vec_cg_back0(xg_w, gn, yn, True)
+    oracle.vec_cg_back1(yg_w, gn, xn, True)
+    gv = G.backend.SO3vec.view([dev(t) for t in g.values()])
+    xg = [torch.zeros(t.shape, dtype=torch.complex64, device="cuda") for t in x.values()]
+    yg = [torch.zeros(t.shape, dtype=torch.complex64, device="cuda") for t in y.values()]
+    G.backend.SO3vec.addDiagCGproduct_back01(G.backend.SO3vec.view(xg), G.backend.SO3vec.view(yg), gv, xv, yv)
+    xg2, yg2 = [torch.zeros_like(t) for t in xg], [torch.zeros_like(t) for t in yg]
+    G.backend.SO3vec.view(xg2).addDiagCGproduct_back0(gv, yv)
+    G.backend.SO3vec.view(yg2).addDiagCGproduct_back1(gv, xv)
+    for a, a2, w in zip(xg, xg2, xg_w.values()):
+        assert rel_err(a, w) < TOL_BIG and rel_err(a2, w) < TOL_BIG
+    for a, a2, w in zip(yg, yg2, yg_w.values()):
+        assert rel_err(a, w) < TOL_BIG and rel_err(a2, w) < TOL_BIG
+
+
+def test_vec_arr_product_values(G, oracle):
+    """SO3vecArr products on a [3] grid are independent products per (batch, grid) cell: values of the full and of
+    the diagonal product and the gradients through autograd, against the oracle on the flattened cells."""
+    torch.manual_seed(9)
+    tau = {0: 2, 1: 3, 2: 2}
+    B, Gd = 2, 3
+    u, v = G.SO3vecArr.randn(B, [Gd], tau, device="cuda"), G.SO3vecArr.randn(B, [Gd], tau, device="cuda")
+    un = {l: np_c(p.reshape(B * Gd, 2 * l + 1, -1)) for l, p in u.parts.items()}
+    vn = {l: np_c(p.reshape(B * Gd, 2 * l + 1, -1)) for l, p in v.parts.items()}
+    for diag in (False, True):
+        if diag:
+            tau_d = {l: 2 for l in range(3)}
+            ud, vd = G.SO3vecArr.randn(B, [Gd], tau_d, device="cuda"), G.SO3vecArr.randn(B, [Gd], tau_d, device="cuda")
+            a, b = ud, vd
+            an = {l: np_c(p.reshape(B * Gd, 2 * l + 1, -1)) for l, p in a.parts.items()}
+            bn = {l: np_c(p.reshape(B * Gd, 2 * l + 1, -1)) for l, p in b.parts.items()}
+            tx = tau_d
+        else:
+            a, b, an, bn, tx = u, v, un, vn, tau
+        a.requires_grad_()
+        b.requires_grad_()
+        w = (G.DiagCGproduct if diag else G.CGproduct)(a, b, maxl=2)
+        tau_r = oracle.cg_type(tx, tx, 2, diag)
+        want = {l: np.zeros((B * Gd, 2 * l + 1, n), np.complex64) for l, n in tau_r.items()}
+        oracle.vec_cg(want, an, bn, diag)
+        for l, wl in want.items():
+            assert list(w.parts[l].shape) == [B, Gd, 2 * l + 1, tau_r[l]]
+            assert rel_err(w.parts[l].reshape(B * Gd, 2 * l + 1, -1), wl) < TOL
+        gvec = type(w).randn_like(w)
+        w.odot(gvec).backward()
+        gn = {l: np_c(p.reshape(B * Gd, 2 * l + 1, -1)) for l, p in gvec.parts.items()}
+        ag_w = {l: np.zeros(t.shape, np.complex64) for l, t in an.items()}
+        bg_w = {l: np.zeros(t.shape, np.complex64) for l, t in bn.items()}
+        oracle.vec_cg_back0(ag_w, gn, bn, diag)
+        oracle.vec_cg_back1(bg_w, gn, an, diag)
+        for l in tx:
+            assert rel_err(a.parts[l].grad.reshape(B * Gd, 2 * l + 1, -1), ag_w[l]) < TOL
+            assert rel_err(b.parts[l].grad.reshape(B * Gd, 2 * l + 1, -1), bg_w[l]) < TOL
+
+
+def test_part_beyond_2_to_31_floats(G, oracle, opt):
+    """64-bit addressing: part l = 4 of the headline output at batch 4096 holds 4096 x 9 x 33792 complex numbers =
+    2.49e9 floats (the reference's GPUtensor carries int32 strides, cuda/GPUtensor.hpp:19-20).  One triple
+    (6,6)->4 is written into and read back from the last 1024 channels; the LAST batch rows, whose float offsets
+    lie beyond 2^31, are compared with the oracle."""
+    B, n, l1, l2, l, ntot = 4096, 32, 6, 6, 4, 33792
+    if torch.cuda.mem_get_info()[0] < 14e9:
+        pytest.skip("needs 10 GB of device memory")
+    offs = ntot - n * n
+    x, y = crandn(61, B, 2 * l1 + 1, n), crandn(62, B, 2 * l2 + 1, n)
+    xd, yd = dev(x), dev(y)
+    big = torch.zeros(B, 2 * l + 1, ntot, dtype=torch.complex64, device="cuda")
+    assert big.numel() * 2 > 2 ** 31
+    want = np.zeros((2, 2 * l + 1, n * n), np.complex64)
+    oracle.add_CGproduct(want, np_c(x[-2:]), np_c(y[-2:]))
+    view(G, big).add_CGproduct(view(G, xd), view(G, yd), offs)
+    assert rel_err(big[-2:, :, offs:], want) < TOL
+    assert float(big[-2:, :, offs - 8:offs].abs().max()) == 0.0
+    # the same block as an upstream gradient: both backward kernels read rows past 2^31 floats
+    gl = crandn(63, 2, 2 * l + 1, n * n)
+    big[-2:, :, offs:] = dev(gl)
+    xg_w, yg_w = np.zeros((2, 2 * l1 + 1, n), np.complex64), np.zeros((2, 2 * l2 + 1, n), np.complex64)
+    oracle.add_CGproduct_back0(xg_w, np_c(gl), np_c(y[-2:]), offs=0)
+    oracle.add_CGproduct_back1(yg_w, np_c(gl), np_c(x[-2:]), offs=0)
+    for kernel in ("pair!", "simt"):
+        opt("bwd", kernel)
+        xg, yg = torch.zeros_like(xd), torch.zeros_like(yd)
+        G.backend.SO3part.add_CGproduct_back01(view(G, xg), view(G, yg), view(G, big), view(G, xd), view(G, yd), offs)
+        assert rel_err(xg[-2:], xg_w) < TOL_BIG and rel_err(yg[-2:], yg_w) < TOL_BIG, kernel
+    del big
+    torch.cuda.empty_cache()
 
 
 # ---- spherical harmonics --------------------------------------------------------------------------------
