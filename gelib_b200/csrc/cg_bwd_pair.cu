@@ -16,7 +16,7 @@
 // the operand-row reads).
 //
 // Organisation.  One CTA per cell; x and y rows and the gradient accumulators of the cell live in shared memory.
-// A producer warp walks a list of groups -- (pair, 32 x 32 channel tile, row m, up to four output l) -- and brings
+// Four copy warps (one per scheduler) walk a list of groups -- (pair, 32 x 32 channel tile, row m, up to four output l) -- and bring
 // the slabs g_l[m] of a group (32 rows of 256 bytes each), the group's coefficients and its two consumer descriptors
 // into a four-stage ring with 16-byte asynchronous copies (cp.async, completion counted on an mbarrier; slab rows
 // padded to 272 bytes so both read patterns are conflict-free; one bulk copy per row was tried first and was
@@ -47,7 +47,8 @@ namespace {
 using namespace tc;
 
 constexpr int kConsumers = 8;                        // 2 roles x 4 quarter tiles
-constexpr int kThreads = (kConsumers + 1) * 32;      // + the producer warp
+constexpr int kProducers = 4;                        // copy warps, one per scheduler; each moves a quarter of every slab
+constexpr int kThreads = (kConsumers + kProducers) * 32;
 constexpr int kRowPitch = 272;                       // bytes per staged slab row: 32 complex + 16
 constexpr int kSlotBytes = 32 * kRowPitch;           // one slab
 constexpr int kGroupSlabs = 4;                       // slabs per group
@@ -70,7 +71,7 @@ struct PairArgs {
   // seven int4 per group.  [0..1] descriptor of the xg warps, [2..3] of the yg warps:
   //   {nslab | band length<<8 | last<<16 | accumulator rows of the pair<<24,
   //    byte offset in shared memory of the other operand's row for the first band entry (tile column 0),
-  //    its signed step in bytes, accumulator row of the first entry, its step (+1 / -1),
+  //    its signed step in bytes, byte offset of the first entry's row in a warp's private rows, its step (+-256),
   //    float offset of the pair-tile's rows in the CTA accumulators, their pitch in floats, 0}
   // [4..6] for the producer:
   //   {nslab | band length<<8 | n2<<16, index of the first coefficient quad, 4 x {ri | (m+l)<<8, first channel of the
@@ -129,39 +130,50 @@ __device__ __forceinline__ void contract(const float (&G)[kGroupSlabs][16], cons
   }
 }
 
-// The band of one group for one warp, two entries per trip so that the loads of one hide behind the arithmetic of the
-// other.  G: the warp's quarter of the group's slabs; coef: the group's coefficient quads; o: the other operand's row
-// chunk for the first entry (4 x 16 bytes), ostep its signed step in 16-byte units; a: the lane's slot in the warp's
-// private accumulator row of the first entry, astep its signed step in 8-byte units.
+// The band of one group for one warp.  The loads of entry k+1 are issued before the arithmetic of entry k (two
+// register sets, used alternately).  All positions are byte offsets into the CTA's shared memory.
+// G: the warp's quarter of the group's slabs; coef: the group's coefficient quads; o: the other operand's row chunk
+// for the first entry (4 x 16 bytes), ostep its signed step; a: the lane's slot in the warp's private accumulator
+// row of the first entry, astep its signed step.
+struct BandEntry {
+  float4 c, w[4];
+};
+__device__ __forceinline__ void load_entry(BandEntry& e, const unsigned char* smem, int coef, int o) {
+  e.c = *reinterpret_cast<const float4*>(smem + coef);
+#pragma unroll
+  for (int t = 0; t < 4; t++) e.w[t] = *reinterpret_cast<const float4*>(smem + o + 16 * t);
+}
 template <int LM>
-__device__ __forceinline__ void band_loop(const float (&G)[kGroupSlabs][16], const float4* coef, int cnt, const float4* o,
-                                          int ostep, float2* a, int astep) {
+__device__ __forceinline__ void use_entry(const float (&G)[kGroupSlabs][16], const BandEntry& e, unsigned char* smem, int a) {
+  float2 s = *reinterpret_cast<float2*>(smem + a);
+  float r, i;
+  contract<LM>(G, e.c, e.w, r, i);
+  s.x += r;
+  s.y += i;
+  *reinterpret_cast<float2*>(smem + a) = s;
+}
+template <int LM>
+__device__ __forceinline__ void band_loop(const float (&G)[kGroupSlabs][16], unsigned char* smem, int coef, int cnt, int o,
+                                          int ostep, int a, int astep) {
+  BandEntry A, B;
+  load_entry(A, smem, coef, o);
   int k = 0;
-  for (; k + 1 < cnt; k += 2) {
-    const float4 c0 = coef[k], c1 = coef[k + 1];
-    const float4* o1 = o + ostep;
-    float2* a1 = a + astep;
-    const float4 w0[4] = {o[0], o[1], o[2], o[3]};
-    const float4 w1[4] = {o1[0], o1[1], o1[2], o1[3]};
-    float2 s0 = *a, s1 = *a1;
-    float r0, i0, r1, i1;
-    contract<LM>(G, c0, w0, r0, i0);
-    contract<LM>(G, c1, w1, r1, i1);
-    s0.x += r0; s0.y += i0;
-    s1.x += r1; s1.y += i1;
-    *a = s0;
-    *a1 = s1;
-    o = o1 + ostep;
-    a = a1 + astep;
+  for (; k + 2 < cnt; k += 2) {
+    load_entry(B, smem, coef + 16, o + ostep);
+    use_entry<LM>(G, A, smem, a);
+    coef += 32;
+    o += 2 * ostep;
+    load_entry(A, smem, coef, o);
+    use_entry<LM>(G, B, smem, a + astep);
+    a += 2 * astep;
   }
-  if (k < cnt) {
-    const float4 c0 = coef[k];
-    const float4 w0[4] = {o[0], o[1], o[2], o[3]};
-    float2 s0 = *a;
-    float r0, i0;
-    contract<LM>(G, c0, w0, r0, i0);
-    s0.x += r0; s0.y += i0;
-    *a = s0;
+  // one or two entries are left, the first of them loaded
+  if (k + 1 < cnt) {
+    load_entry(B, smem, coef + 16, o + ostep);
+    use_entry<LM>(G, A, smem, a);
+    use_entry<LM>(G, B, smem, a + astep);
+  } else {
+    use_entry<LM>(G, A, smem, a);
   }
 }
 
@@ -220,7 +232,7 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NS; s++) {
-      mbar_init(&full[s], 32);          // one arrival per producer lane, when that lane's copies have landed
+      mbar_init(&full[s], 32 * kProducers);  // one arrival per producer lane, when that lane's copies have landed
       mbar_init(&empty[s], kConsumers);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -235,43 +247,65 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
   for (int e = threadIdx.x; e < A.cell_floats + kConsumers * J * 64; e += blockDim.x) acc_f[e] = 0.f;  // + priv
   __syncthreads();
 
-  if (warp == kConsumers) {
-    // ---- producer: 16-byte asynchronous copies, a group per stage.  Lane t moves chunk t of two rows at a time
-    // (global reads of 512 contiguous bytes per instruction), 16 instructions per slab.
+  if (warp >= kConsumers) {
+    // ---- producers: 16-byte asynchronous copies, a group per stage.  Lane t moves chunk t of two rows at a time
+    // (global reads of 512 contiguous bytes per instruction); a slab takes 16 such instructions, four per warp.
+    const int pw = warp - kConsumers;
     bool ok = true;
-    int4 p0 = make_int4(0, 0, 0, 0), p1 = p0, p2 = p0;
-    if (A.ngroups > 0) {
-      p0 = __ldg(&A.recs[4]); p1 = __ldg(&A.recs[5]); p2 = __ldg(&A.recs[6]);
-    }
-    const int half = lane >> 4, cc = lane & 15;
+    // Records are fetched 32 groups at a time, one group per lane, a batch ahead of their use, and handed round
+    // with shuffles: the latency of the loads is paid once per batch, off the copy loop.
+    auto fetch = [&](int g, int4& b0, int4& b1, int4& b2) {
+      const int gg = g < A.ngroups ? g : A.ngroups - 1;
+      b0 = __ldg(&A.recs[kRec * gg + 4]); b1 = __ldg(&A.recs[kRec * gg + 5]); b2 = __ldg(&A.recs[kRec * gg + 6]);
+    };
+    int4 b0 = make_int4(0, 0, 0, 0), b1 = b0, b2 = b0, nb0 = b0, nb1 = b0, nb2 = b0;
+    if (A.ngroups > 0) fetch(lane, b0, b1, b2);
+    const int rowi = 8 * pw + (lane >> 4), cc = lane & 15;   // first row this lane copies, and its 16-byte chunk
     const uint32_t ring_a = smem_u32(ring);
+    int st = 0, phase = 0;
+    bool first_round = true;
     for (int gi = 0; gi < A.ngroups; gi++) {
-      const int st = gi % NS, round = gi / NS;
-      // the next record is on its way while this group is issued
-      const int gn = gi + 1 < A.ngroups ? gi + 1 : gi;
-      const int4 n0 = __ldg(&A.recs[kRec * gn + 4]), n1 = __ldg(&A.recs[kRec * gn + 5]), n2r = __ldg(&A.recs[kRec * gn + 6]);
-      if (round > 0) ok = mbar_wait(&empty[st], (round - 1) & 1);
+      const int k = gi & 31;
+      if (k == 0 && gi + 32 < A.ngroups) fetch(gi + 32 + lane, nb0, nb1, nb2);
+      int4 p0, p1, p2;
+      p0.x = __shfl_sync(0xffffffffu, b0.x, k); p0.y = __shfl_sync(0xffffffffu, b0.y, k);
+      p0.z = __shfl_sync(0xffffffffu, b0.z, k); p0.w = __shfl_sync(0xffffffffu, b0.w, k);
+      p1.x = __shfl_sync(0xffffffffu, b1.x, k); p1.y = __shfl_sync(0xffffffffu, b1.y, k);
+      p1.z = __shfl_sync(0xffffffffu, b1.z, k); p1.w = __shfl_sync(0xffffffffu, b1.w, k);
+      p2.x = __shfl_sync(0xffffffffu, b2.x, k); p2.y = __shfl_sync(0xffffffffu, b2.y, k);
+      if (!first_round) ok = mbar_wait(&empty[st], phase ^ 1);
       if (!ok) break;
       const int nslab = p0.x & 7, cnt = (p0.x >> 8) & 0xff, n2 = (p0.x >> 16) & 0xffff;
       const uint32_t sbase = ring_a + st * kStageBytes;
       const int sw[8] = {p0.z, p0.w, p1.x, p1.y, p1.z, p1.w, p2.x, p2.y};
+      {
 #pragma unroll
-      for (int s = 0; s < kGroupSlabs; s++) {
-        if (s < nslab) {
-          const int ri = sw[2 * s] & 0xff, row = sw[2 * s] >> 8;
-          const PartView& gp = A.g[ri];
-          const float* src = gp.base + goff[ri] + (long long)row * gp.sm +
-                             2LL * ((long long)sw[2 * s + 1] + A.offs_extra + (long long)half * n2) + 4 * cc;
-          const uint32_t dst = sbase + s * kSlotBytes + half * kRowPitch + cc * 16;
-          const long long step = 4LL * n2;  // two rows of the part, in floats
+        for (int s = 0; s < kGroupSlabs; s++) {
+          if (s < nslab) {
+            const int ri = sw[2 * s] & 0xff, row = sw[2 * s] >> 8;
+            const PartView& gp = A.g[ri];
+            const float* src = gp.base + goff[ri] + (long long)row * gp.sm +
+                               2LL * ((long long)sw[2 * s + 1] + A.offs_extra + (long long)rowi * n2) + 4 * cc;
+            const uint32_t dst = sbase + s * kSlotBytes + rowi * kRowPitch + cc * 16;
+            const long long step = 4LL * n2;  // two rows of the part, in floats
 #pragma unroll
-          for (int it = 0; it < 16; it++) cp_async16(dst + it * 2 * kRowPitch, src + it * step);
+            for (int it = 0; it < 16 / kProducers; it++) cp_async16(dst + it * 2 * kRowPitch, src + it * step);
+          }
         }
       }
-      if (lane < cnt) cp_async16(sbase + kCoefOff + lane * 16, A.coef + p0.y + lane);
-      if (lane < 4) cp_async16(sbase + kDescOff + lane * 16, &A.recs[kRec * gi + lane]);
+      if (pw == 0) {
+        if (lane < cnt) cp_async16(sbase + kCoefOff + lane * 16, A.coef + p0.y + lane);
+        if (lane < 4) cp_async16(sbase + kDescOff + lane * 16, &A.recs[kRec * gi + lane]);
+      }
       if (gi != A.skip_group) cp_async_arrive(&full[st]);
-      p0 = n0; p1 = n1; p2 = n2r;
+      if (++st == NS) {
+        st = 0;
+        phase ^= 1;
+        first_round = false;
+      }
+      if (k == 31) {
+        b0 = nb0; b1 = nb1; b2 = nb2;
+      }
     }
     cp_async_wait_all();  // nothing of this warp is in flight when the CTA gives its shared memory back
     if (!ok && lane == 0) *A.status = 1;
@@ -280,13 +314,14 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
     const int role = warp >> 2, q = warp & 3;
     const bool active = role == 0 ? (A.do_x != 0) : (A.do_y != 0);
     float2* mine = priv + (warp * J) * 32 + lane;
+    const int mine_off = kHeaderBytes + 8 * A.cell_floats + (warp * J * 32 + lane) * 8;  // the same as a byte offset
     // where the warp's quarter of a slab sits inside a slot: xg warps read row `lane`, columns 8q..8q+7 (16-byte
     // loads, lanes 272 bytes apart); yg warps read rows 8q..8q+7, column `lane` (8-byte loads, lanes adjacent)
     const int goffs = role == 0 ? lane * kRowPitch + q * 64 : 8 * q * kRowPitch + lane * 8;
     bool ok = true;
+    int st = 0, phase = 0;
     for (int gi = 0; gi < A.ngroups; gi++) {
-      const int st = gi % NS, round = gi / NS;
-      ok = mbar_wait(&full[st], round & 1);
+      ok = mbar_wait(&full[st], phase);
       if (!ok) break;
       if (active) {
         const unsigned char* sbase = ring + st * kStageBytes;
@@ -319,16 +354,13 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
             }
           }
         }
-        const float4* coef = reinterpret_cast<const float4*>(sbase + kCoefOff);
-        const float4* o = reinterpret_cast<const float4*>(smem_raw + d0.y + q * 64);
-        const int ostep = d0.z >> 4;
-        float2* a = mine + d0.w * 32;
-        const int astep = d1.x * 32;
+        const int sb = ring_off + st * kStageBytes;
+        const int o = d0.y + q * 64, a = mine_off + d0.w;
         switch (nslab) {
-          case 1: band_loop<1>(G, coef, cnt, o, ostep, a, astep); break;
-          case 2: band_loop<2>(G, coef, cnt, o, ostep, a, astep); break;
-          case 3: band_loop<3>(G, coef, cnt, o, ostep, a, astep); break;
-          default: band_loop<4>(G, coef, cnt, o, ostep, a, astep); break;
+          case 1: band_loop<1>(G, smem_raw, sb + kCoefOff, cnt, o, d0.z, a, d1.x); break;
+          case 2: band_loop<2>(G, smem_raw, sb + kCoefOff, cnt, o, d0.z, a, d1.x); break;
+          case 3: band_loop<3>(G, smem_raw, sb + kCoefOff, cnt, o, d0.z, a, d1.x); break;
+          default: band_loop<4>(G, smem_raw, sb + kCoefOff, cnt, o, d0.z, a, d1.x); break;
         }
         if (d0.x & 0x10000) {  // last group of the pair-tile: the warp's partial rows go to the CTA's accumulators
           const int rows = (d0.x >> 24) & 0xff;
@@ -343,6 +375,10 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[st]);  // the stage (slabs, coefficients, descriptors) is free again
+      if (++st == NS) {
+        st = 0;
+        phase ^= 1;
+      }
     }
     if (!ok && lane == 0) *A.status = 1;
   }
@@ -433,12 +469,12 @@ int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s) {
               const int head = nslab | (cnt << 8);
               // xg warps: y rows downwards from m2 = m - lo, accumulator rows upwards from m1 = lo
               p.h_items.push_back(make_int4(head | ((2 * l1 + 1) << 24), kHeaderBytes + 4 * (yoff[yi] + 2 * b0 + 2 * n2 * j2hi),
-                                            -8 * n2, jlo));
-              p.h_items.push_back(make_int4(1, xoff[xi] + 2 * a0, 2 * n1, 0));
+                                            -8 * n2, 256 * jlo));
+              p.h_items.push_back(make_int4(256, xoff[xi] + 2 * a0, 2 * n1, 0));
               // yg warps: x rows upwards from m1 = lo, accumulator rows downwards from m2 = m - lo
               p.h_items.push_back(make_int4(head | ((2 * l2 + 1) << 24), kHeaderBytes + 4 * (xoff[xi] + 2 * a0 + 2 * n1 * jlo),
-                                            8 * n1, j2hi));
-              p.h_items.push_back(make_int4(-1, yoff[yi] + 2 * b0, 2 * n2, 0));
+                                            8 * n1, 256 * j2hi));
+              p.h_items.push_back(make_int4(-256, yoff[yi] + 2 * b0, 2 * n2, 0));
               p.h_items.push_back(make_int4(head | (n2 << 16), (int)(quads.size() / 4), sw[0], sw[1]));
               p.h_items.push_back(make_int4(sw[2], sw[3], sw[4], sw[5]));
               p.h_items.push_back(make_int4(sw[6], sw[7], 0, 0));
