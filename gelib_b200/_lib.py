@@ -53,6 +53,7 @@ SYMBOLS = {
     "gelib_SO3part_addDiagCGproduct_back01": (ctypes.c_int, _PART5),
     "gelib_SO3part_addSPharm": (ctypes.c_int, [_P5, _P5, ctypes.c_int, ctypes.c_void_p]),
     "gelib_SO3vec_addCGproduct": (ctypes.c_int, _VEC3),
+    "gelib_SO3vec_addCGproduct_static": (ctypes.c_int, _VEC3),
     "gelib_SO3vec_addCGproduct_back0": (ctypes.c_int, _VEC3),
     "gelib_SO3vec_addCGproduct_back1": (ctypes.c_int, _VEC3),
     "gelib_SO3vec_addCGproduct_back01": (ctypes.c_int, _VEC5),

@@ -194,6 +194,11 @@ class SO3vec:
     def addCGproduct(self, x, y, *, overwrite=False):
         return self._call3("gelib_SO3vec_addCGproduct", self, x, y, GELIB_OVERWRITE if overwrite else 0)
 
+    def addCGproduct_static(self, x, y, *, overwrite=False):
+        """addCGproduct through the entry point that allocates no device memory (tables in a fixed 64 KB device
+        array shared by all calls: do not let two such calls overlap on the GPU)."""
+        return self._call3("gelib_SO3vec_addCGproduct_static", self, x, y, GELIB_OVERWRITE if overwrite else 0)
+
     def addCGproduct_back0(self, g, y):
         return self._call3("gelib_SO3vec_addCGproduct_back0", self, g, y)
 

@@ -134,7 +134,7 @@ int check_room(const char* fn, const std::vector<PartView>& x, const std::vector
 // mode 0: forward (out = r).  mode 1/2/3: gradient wrt x / y / both (r is g).
 int run_product(const char* fn, bool diag, int mode, int nr, const gelib_tensor5* r, int nx, const gelib_tensor5* x,
                 int ny, const gelib_tensor5* y, int nxg, const gelib_tensor5* xg, int nyg, const gelib_tensor5* yg,
-                int offs, int flags, void* stream, bool single_triple) {
+                int offs, int flags, void* stream, bool single_triple, bool no_alloc = false) {
   VecCall c;
   c.diag = diag;
   c.flags = flags;
@@ -205,6 +205,7 @@ int run_product(const char* fn, bool diag, int mode, int nr, const gelib_tensor5
     return fail(GELIB_INVALID, fn, "GELIB_OVERWRITE with an output that is broadcast over cells (the cells are summed into it)");
 
   cudaStream_t s = (cudaStream_t)stream;
+  if (no_alloc) return launch_cg_strided_static(c, s);
   if (mode == 0) {
     st = -1;
     if (c.dense_channels && !c.r_bcast) {
@@ -399,6 +400,12 @@ int gelib_SO3vec_addDiagCGproduct_back01(int nx, const gelib_tensor5* xg, int ny
                                          const gelib_tensor5* g, const gelib_tensor5* x, const gelib_tensor5* y,
                                          int flags, void* stream) {
   return run_product("SO3vec_addDiagCGproduct_back01", true, 3, ng, g, nx, x, ny, y, nx, xg, ny, yg, 0, flags, stream, false);
+}
+
+int gelib_SO3vec_addCGproduct_static(int nr, const gelib_tensor5* r, int nx, const gelib_tensor5* x, int ny,
+                                     const gelib_tensor5* y, int flags, void* stream) {
+  return run_product("SO3vec_addCGproduct_static", false, 0, nr, r, nx, x, ny, y, 0, nullptr, 0, nullptr, 0, flags, stream, false,
+                     true);
 }
 
 // ---- spherical harmonics ------------------------------------------------------------------------------------

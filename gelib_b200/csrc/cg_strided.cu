@@ -5,6 +5,9 @@
 // into the same memory, core/Gpart.hpp:168-185 of GElib).  One CTA handles one (cell, triple); a
 // thread owns one output element and walks the band.  Gradients are combined with atomicAdd because
 // several triples (and, for broadcast outputs, several cells) contribute to one element.
+#include <cstring>
+#include <mutex>
+
 #include "plan.h"
 
 namespace gelib_b200 {
@@ -149,6 +152,84 @@ int launch_cg_strided(const VecCall& c, int mode, cudaStream_t s) {
   if (mode == 0) cg_strided_kernel<0><<<grid, 256, 0, s>>>(a);
   else if (mode == 1) cg_strided_kernel<1><<<grid, 256, 0, s>>>(a);
   else cg_strided_kernel<2><<<grid, 256, 0, s>>>(a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return check_cuda(e, fn, "strided kernel launch");
+  count_launch();
+  return GELIB_OK;
+}
+
+// ---- the forward product without any allocation ---------------------------------------------------------------
+//
+// Every other launcher keeps its tables (triple list, band coefficients) in device memory that the plan cache gets
+// from cudaMalloc on the first call of a product signature.  A caller that must not allocate -- one that runs inside
+// a memory pool it may not leave, under a real-time budget where cudaMalloc's implicit synchronisation is not
+// acceptable, or after it has handed all device memory to somebody else -- uses this variant instead: the same
+// kernel, with the tables in a fixed array that is part of the library's image on every device that loads it.
+//
+// The array is shared by all calls on a device and keeps the tables of the last call: each call uploads its own
+// tables on the caller's stream before its kernel, so calls on ONE stream are ordered, and calls that can overlap on
+// the GPU (different streams, different threads) race on the array and must be serialised by the caller.
+namespace {
+
+constexpr size_t kStaticTableBytes = 64 * 1024;  // 175 triples + 7651 coefficients (maxl 6) take 34 KB
+__device__ __align__(256) unsigned char g_static_tables[kStaticTableBytes];
+
+// Device address of g_static_tables on the current device.  In host code the array's name is only a handle; the
+// address a kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.
+unsigned char* static_tables_address() {
+  static std::mutex mu;
+  static unsigned char* addr[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!addr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_tables) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    addr[dev] = static_cast<unsigned char*>(p);
+  }
+  return addr[dev];
+}
+
+}  // namespace
+
+int launch_cg_strided_static(const VecCall& c, cudaStream_t s) {
+  static const char* fn = "SO3vec_addCGproduct_static";
+  Schedule sched;  // host memory only
+  build_schedule(sig_of(c.x), sig_of(c.y), sig_of(c.r), c.diag, true, &sched);
+  const size_t ntr = sched.triples.size();
+  if (ntr == 0 || c.cg.ncells == 0) return GELIB_OK;
+  if (ntr > 65535) return fail(GELIB_SKIPPED, fn, "more than 65535 triples");
+  if (c.cg.ncells > 0x7fffffffLL) return fail(GELIB_SKIPPED, fn, "number of cells exceeds 2^31-1");
+  const size_t tbytes = (ntr * sizeof(Triple) + 15) / 16 * 16, cbytes = sched.coeffs.size() * sizeof(float);
+  if (tbytes + cbytes > kStaticTableBytes)
+    return fail(GELIB_INVALID, fn, "the tables of this product need " + std::to_string(tbytes + cbytes) +
+                                       " bytes, the static array holds " + std::to_string(kStaticTableBytes));
+  unsigned char* dev = static_tables_address();
+  if (!dev) return fail(GELIB_CUDA_ERROR, fn, "cudaGetSymbolAddress failed for the static table array");
+  // one upload: [triples | coefficients]; pageable source, so the copy has left this buffer when the call returns
+  std::vector<unsigned char> host(tbytes + cbytes);
+  memcpy(host.data(), sched.triples.data(), ntr * sizeof(Triple));
+  memcpy(host.data() + tbytes, sched.coeffs.data(), cbytes);
+  GELIB_CUDA_TRY(fn, cudaMemcpyAsync(dev, host.data(), host.size(), cudaMemcpyHostToDevice, s));
+
+  StridedArgs a;
+  for (size_t i = 0; i < c.x.size(); i++) a.x[i] = c.x[i];
+  for (size_t i = 0; i < c.y.size(); i++) a.y[i] = c.y[i];
+  for (size_t i = 0; i < c.r.size(); i++) a.r[i] = c.r[i];
+  a.cg = c.cg;
+  a.triples = reinterpret_cast<const Triple*>(dev);
+  a.coeffs = reinterpret_cast<const float*>(dev + tbytes);
+  a.offs_extra = c.offs_extra;
+  a.diag = c.diag ? 1 : 0;
+  a.atomic_out = c.r_bcast ? 1 : 0;
+  a.overwrite = (c.flags & GELIB_OVERWRITE) && !c.r_bcast ? 1 : 0;
+  cg_strided_kernel<0><<<dim3((unsigned)c.cg.ncells, (unsigned)ntr), 256, 0, s>>>(a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return check_cuda(e, fn, "strided kernel launch");
   count_launch();

@@ -37,6 +37,7 @@ int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s);  // uncoupled-gradient
 int launch_cg_narrow_bwd(const VecCall& c, cudaStream_t s);
 int launch_cg_narrow_fwd(const VecCall& c, cudaStream_t s);  // x with at most 4 channels; -1 when the call does not qualify
 int launch_cg_strided(const VecCall& c, int mode, cudaStream_t s);  // mode 0 fwd, 1 back0, 2 back1
+int launch_cg_strided_static(const VecCall& c, cudaStream_t s);  // forward, tables in a static device array: no allocation
 int launch_diag_fwd(const VecCall& c, cudaStream_t s);
 int launch_diag_bwd(const VecCall& c, cudaStream_t s);
 int launch_diag_fwd_fast(const VecCall& c, cudaStream_t s);  // -1 when the call does not qualify

@@ -142,6 +142,31 @@ int gelib_SO3vec_addDiagCGproduct_back01(int nx, const gelib_tensor5* xg, int ny
                                          int ng, const gelib_tensor5* g, const gelib_tensor5* x,
                                          const gelib_tensor5* y, int flags, void* stream);
 
+/* The forward product of gelib_SO3vec_addCGproduct for callers that must not allocate device memory.  (No counterpart
+ * in the reference: this entry point exists only here.)
+ *
+ * Every other product call keeps its tables (triple list, Clebsch-Gordan coefficients) in device memory that the library
+ * takes from cudaMalloc the first time it sees a product signature.  Some callers cannot have that: a plug-in that runs
+ * inside a framework's memory pool and may not go around it, a service whose device memory has all been handed out
+ * before the first request, a latency-bound loop in which cudaMalloc's implicit device synchronisation is not tolerable.
+ * This variant runs the general strided kernel with its tables in a fixed 64 KB array that is part of the library image
+ * on every GPU that loads it (the memory is held until the process exits, used or not).  It calls no cudaMalloc, no
+ * cudaFree and no other allocating routine; inputs and outputs are the caller's, as everywhere else.
+ *
+ * Limits and rules:
+ *  - the product's tables (20 bytes per (l1,l2)->l triple, rounded up to 16, plus 4 bytes per band coefficient) must
+ *    fit 65536 bytes, else GELIB_INVALID with the needed size in gelib_last_error() (maxl 6 with 7 parts on either side
+ *    needs 34 KB);
+ *  - the first call on a device looks the array's device address up (cudaGetSymbolAddress, with that device current);
+ *    make that first call outside any stream capture;
+ *  - every call uploads its own tables into the shared array on `stream` before its kernel, so calls on one stream are
+ *    ordered, but two calls that can overlap on the GPU (different streams or threads) race on the array: serialise them;
+ *  - it is the correctness kernel (one thread per output element), not the tiled one: expect a fraction of the speed of
+ *    gelib_SO3vec_addCGproduct.
+ * Arguments, flags, status codes and results are those of gelib_SO3vec_addCGproduct. */
+int gelib_SO3vec_addCGproduct_static(int nr, const gelib_tensor5* r, int nx, const gelib_tensor5* x, int ny,
+                                     const gelib_tensor5* y, int flags, void* stream);
+
 /* Spherical harmonics of every part r[i] (any set of l) from one read of x and one Legendre recursion
  * per point; equivalent to one gelib_SO3part_addSPharm call per part (the per-l loop a caller of
  * SO3part.spharm writes, python/src/gelib/SO3part.py:54-62). */
