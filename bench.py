@@ -71,10 +71,15 @@ def algorithmic_work(tx, ty, maxl, B, diag):
     return {"macs": macs * B, "fwd_bytes": 8 * B * (xin + rout), "bwd_bytes": 8 * B * (rout + 2 * xin), "tau_r": out}
 
 
-# DRAM traffic of one launch relative to its algorithmic bytes, from the ncu captures summarised in
-# profiles/cg_fwd_kernel_cfg3_b296.md and profiles/cg_bwd_kernel_cfg3_b296.md (dram__bytes_read + dram__bytes_write of
-# a batch-296 launch; traffic grows in proportion to the batch, so the ratio carries over to the full batch).
-TRAFFIC_RATIO = {("cfg3", "forward"): 0.98, ("cfg3", "backward"): 1.002}
+# DRAM traffic of one launch relative to its algorithmic bytes: dram__bytes_read + dram__bytes_write of one ncu capture
+# of a batch-296 launch of the named kernel (every cell reads and writes its own rows once, so traffic grows in
+# proportion to the batch and the ratio carries over).  A kernel without a capture reports traffic null.
+TRAFFIC_RATIO = {
+    "cg_fwd_tc_kernel": (0.98, "cfg3, batch 296, ncu 2025.2 --set full"),
+    "cg_fwd_kernel": (0.98, "cfg3, batch 296, ncu 2025.2 --set full"),
+    "cg_bwd_kernel": (1.002, "cfg3, batch 296, ncu 2025.2 --set full"),
+    "cg_bwd_pair_kernel": (1.0025, "cfg3, batch 296, ncu 2025.2 --set full"),
+}
 
 
 def kernel_name(args, dom):
@@ -186,6 +191,9 @@ def cpu_fwd_bwd(O, tx, ty, maxl, Bs, diag, nthreads, reps=1):
 
 
 def cpu_baseline(tx, ty, maxl, B, diag, budget_s=15.0):
+    """Two CPU legs of the oracle (a restatement of the reference's loops): all host threads (OpenMP over the batch),
+    and one thread, which is the reference's default session size (include/GElibSession.hpp:30,
+    python/bindings/GElib_py.cpp:43).  Both on a slice of the batch, extrapolated linearly (cells are independent)."""
     from oracle import oracle as O
     O.build()
     nt = host_threads()
@@ -197,9 +205,15 @@ def cpu_baseline(tx, ty, maxl, B, diag, budget_s=15.0):
         Bs *= scale
         t = cpu_fwd_bwd(O, tx, ty, maxl, Bs, diag, nt)
     ms_full = t * 1e3 * B / Bs
+    # one thread: a slice sized from the all-threads rate so that it takes a few seconds
+    B1 = int(max(1, min(B, Bs * 4.0 / max(t * nt, 1e-3))))
+    t1 = cpu_fwd_bwd(O, tx, ty, maxl, B1, diag, 1)
     return {"value": ms_full, "unit": "ms", "cores": nt, "kind": "port",
             "sample": "oracle (CPU restatement of the reference loops, OpenMP over the batch) on %d of %d batch rows: "
-                      "%.1f ms measured, extrapolated linearly" % (Bs, B, t * 1e3)}
+                      "%.1f ms measured, extrapolated linearly" % (Bs, B, t * 1e3),
+            "single_thread_ms": t1 * 1e3 * B / B1,
+            "single_thread_sample": "the same loops on 1 thread (the reference's default) on %d of %d batch rows: "
+                                    "%.1f ms measured, extrapolated linearly" % (B1, B, t1 * 1e3)}
 
 
 def run_reference(args, tx, ty, maxl, B, diag, desc):
@@ -221,11 +235,15 @@ def run_reference(args, tx, ty, maxl, B, diag, desc):
     ms = statistics.mean(times) * 1e3 * B / Bs
     cb = {"value": ms, "unit": "ms", "cores": nt, "kind": "port",
           "sample": "oracle on %d of %d batch rows per step, extrapolated linearly" % (Bs, B)}
-    print(json.dumps({"impl": "reference", "metric": "cg_product_fwd_bwd_ms_per_call", "value": ms, "unit": "ms",
+    print(json.dumps({"impl": "reference", "kind": "port", "extrapolated": True, "measured_rows": Bs,
+                      "measured_ms_per_step": statistics.mean(times) * 1e3, "cores": nt,
+                      "metric": "cg_product_fwd_bwd_ms_per_call", "value": ms, "unit": "ms",
                       "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-                      "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-                      "data": "synthetic",
-                      "config": {"workload": "%s: %s; per-GPU batch %d, global batch %d" % (args.workload, desc, B, B * args.gpus)},
+                      "higher_is_better": False, "scaling": "strong" if args.workload == "cfg5" else "weak",
+                      "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "%s: %s; per-GPU batch %d, global batch %d" % (
+                          (args.workload, desc, B // args.gpus, B) if args.workload == "cfg5"
+                          else (args.workload, desc, B, B * args.gpus))},
                       "cpu_baseline": cb,
                       "e2e": {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
@@ -243,6 +261,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-strong", action="store_true", help="skip the extra strong-scaling region of multi-GPU runs")
     ap.add_argument("--bwd-kernel", default="auto", choices=["auto", "simt", "pair", "tcgen05"],
                     help="backward kernel for channel counts that are multiples of 32 (auto = the pair kernel)")
     ap.add_argument("--fwd-kernel", default="auto", choices=["auto", "simt", "tcgen05"],
@@ -256,6 +275,9 @@ def main():
         B = args.batch
     if args.impl == "reference":
         return run_reference(args, tx, ty, maxl, B, diag, desc)
+    strong = args.workload == "cfg5"   # its points are split evenly over the ranks; every other workload is weak
+    if strong:
+        B = B // max(1, int(os.environ.get("WORLD_SIZE", "1")))
 
     import torch
     import torch.distributed as dist
@@ -279,22 +301,65 @@ def main():
     def crandn(*shape):
         return torch.view_as_complex(torch.randn(*shape, 2, device=devc, generator=gen))
 
-    xs = [crandn(B, 2 * l + 1, n) for l, n in tx.items()]
-    ys = [crandn(B, 2 * l + 1, n) for l, n in ty.items()]
-    rs = [torch.empty(B, 2 * l + 1, n, dtype=torch.complex64, device=devc) for l, n in tau_r.items()]
-    gs = [crandn(B, 2 * l + 1, n) for l, n in tau_r.items()]
-    xg = [torch.zeros_like(t) for t in xs]
-    yg = [torch.zeros_like(t) for t in ys]
-    xv, yv, rv, gv = gb.SO3vec.view(xs), gb.SO3vec.view(ys), gb.SO3vec.view(rs), gb.SO3vec.view(gs)
-    xgv, ygv = gb.SO3vec.view(xg), gb.SO3vec.view(yg)
-    fwd = rv.addDiagCGproduct if diag else rv.addCGproduct
-    bwd = gb.SO3vec.addDiagCGproduct_back01 if diag else gb.SO3vec.addCGproduct_back01
+    pipeline = args.workload == "cfg5"
+    if pipeline:
+        # The named pipeline: points on the sphere scaled by radii U(0.5,2) -> spherical harmonics l = 0..6 (1 channel)
+        # -> a 16-channel SO3vec mixed by per-l complex weights N(0,1/sqrt 16) -> full CG product, maxl 6, forward and
+        # backward (gradients reach v and the weights), all through the Python API of gelib_b200.  The product stage is
+        # the C-ABI call pair of the other workloads.
+        d = torch.randn(B, 3, 1, device=devc, generator=gen)
+        X = (d / d.norm(dim=1, keepdim=True) * (0.5 + 1.5 * torch.rand(B, 1, 1, device=devc, generator=gen))).contiguous()
+        xs = [X]                                                   # what travels host -> device in the e2e step
+        ys = [crandn(B, 2 * l + 1, n).requires_grad_() for l, n in ty.items()]
+        Wp = [(crandn(n, n) / 4.0).requires_grad_() for l, n in ty.items()]
+        Wobj = gelib_b200.SO3weights(*Wp)
+        gs = [crandn(B, 2 * l + 1, n) for l, n in tau_r.items()]
+        rs = []
+        xg, yg = [], []
+        state = {}
+
+        def st_spharm():
+            state["u"] = gelib_b200.SO3vec.spharms(maxl, X)
+
+        def st_mix():
+            state["vw"] = gelib_b200.SO3vec(*[gelib_b200.SO3part(t) for t in ys]) * Wobj
+
+        def st_forward():
+            state["z"] = gelib_b200.CGproduct(state["u"], state["vw"], maxl=maxl)
+
+        def st_backward():
+            for t in ys + Wp:
+                t.grad = None
+            torch.autograd.backward(list(state["z"].parts.values()), grad_tensors=gs)
+            state.clear()
+
+        stages = [("spharm", st_spharm), ("mix", st_mix), ("forward", st_forward), ("backward", st_backward)]
+        bwd = None
+    else:
+        xs = [crandn(B, 2 * l + 1, n) for l, n in tx.items()]
+        ys = [crandn(B, 2 * l + 1, n) for l, n in ty.items()]
+        rs = [torch.empty(B, 2 * l + 1, n, dtype=torch.complex64, device=devc) for l, n in tau_r.items()]
+        gs = [crandn(B, 2 * l + 1, n) for l, n in tau_r.items()]
+        xg = [torch.zeros_like(t) for t in xs]
+        yg = [torch.zeros_like(t) for t in ys]
+        xv, yv, rv, gv = gb.SO3vec.view(xs), gb.SO3vec.view(ys), gb.SO3vec.view(rs), gb.SO3vec.view(gs)
+        xgv, ygv = gb.SO3vec.view(xg), gb.SO3vec.view(yg)
+        fwd = rv.addDiagCGproduct if diag else rv.addCGproduct
+        bwd = gb.SO3vec.addDiagCGproduct_back01 if diag else gb.SO3vec.addCGproduct_back01
+
+        def st_forward():
+            fwd(xv, yv, overwrite=True)
+
+        def st_backward():
+            for t in xg + yg:
+                t.zero_()
+            bwd(xgv, ygv, gv, xv, yv)
+
+        stages = [("forward", st_forward), ("backward", st_backward)]
 
     def step():
-        fwd(xv, yv, overwrite=True)
-        for t in xg + yg:
-            t.zero_()
-        bwd(xgv, ygv, gv, xv, yv)
+        for _, f in stages:
+            f()
 
     def sync_all():
         if world > 1:
@@ -307,7 +372,7 @@ def main():
 
     # ---- device-resident timing: per-step events around the forward and the backward launch
     K = args.steps
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(stages) + 1)] for _ in range(K)]
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -316,24 +381,45 @@ def main():
     t_wall = time.perf_counter()
     for k in range(K):
         ev[k][0].record()
-        fwd(xv, yv, overwrite=True)
-        ev[k][1].record()
-        for t in xg + yg:
-            t.zero_()
-        bwd(xgv, ygv, gv, xv, yv)
-        ev[k][2].record()
+        for i, (_, f) in enumerate(stages):
+            f()
+            ev[k][i + 1].record()
     sync_all()
     t_wall = time.perf_counter() - t_wall
     launches = gb.kernel_launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
-    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / K
-    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / K
-    tot_ms = ev[0][0].elapsed_time(ev[-1][2]) / K
+    stage_ms = {name: sum(e[i].elapsed_time(e[i + 1]) for e in ev) / K for i, (name, _) in enumerate(stages)}
+    fwd_ms, bwd_ms = stage_ms["forward"], stage_ms["backward"]
+    tot_ms = ev[0][0].elapsed_time(ev[-1][-1]) / K
 
     # ---- end to end from pinned host buffers
     e2e_ms = None
     h2d = d2h = 0
-    if not args.no_e2e:
+    if not args.no_e2e and pipeline:
+        # host points and host v parts in, gradients of v and of the weights out, every step
+        hin = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t.detach()) for t in [X] + ys]
+        hout = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in ys + Wp]
+        h2d = sum(t.numel() * t.element_size() for t in hin)
+        d2h = sum(t.numel() * t.element_size() for t in hout)
+
+        def e2e_step():
+            with torch.no_grad():
+                for dst, h in zip([X] + ys, hin):
+                    dst.copy_(h, non_blocking=True)
+            step()
+            for h, t in zip(hout, ys + Wp):
+                h.copy_(t.grad, non_blocking=True)
+
+        e2e_step()
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(K):
+            e2e_step()
+        e1.record()
+        sync_all()
+        e2e_ms = e0.elapsed_time(e1) / K
+    elif not args.no_e2e:
         hx = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for t in xs + ys]
         hg = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in xg + yg]
         h2d = sum(t.numel() * 8 for t in hx)
@@ -395,37 +481,91 @@ def main():
     if e2e_ms is not None:
         e2e_ms = reduce_max(e2e_ms)
 
+    # ---- the second roof: FP32 multiply-add rate measured on this device (148 SMs x 8 CTAs of 256 threads)
+    probe_buf = torch.empty(148 * 8 * 256, dtype=torch.float32, device=devc)
+    fp32_peak = float(gelib_b200._lib.lib().gelib_probe_fp32_tflops(probe_buf.data_ptr(), 148 * 8, 3,
+                                                                    torch.cuda.current_stream().cuda_stream))
+
+    # ---- strong scaling: the per-GPU batch of the 1-GPU run split over the ranks (extra key; `value` stays weak)
+    strong_ms = None
+    if world > 1 and B >= world and not args.no_strong and not pipeline:
+        Bq = B // world
+        sl = lambda ts: [t[:Bq] for t in ts]
+        sx, sy, sr, sg, sxg, syg = (gb.SO3vec.view(sl(v)) for v in (xs, ys, rs, gs, xg, yg))
+        sfwd = sr.addDiagCGproduct if diag else sr.addCGproduct
+
+        def sstep():
+            sfwd(sx, sy, overwrite=True)
+            for t in xg + yg:
+                t[:Bq].zero_()
+            bwd(sxg, syg, sg, sx, sy)
+
+        for _ in range(3):
+            sstep()
+        sync_all()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(K):
+            sstep()
+        s1.record()
+        sync_all()
+        strong_ms = reduce_max(s0.elapsed_time(s1) / K)
+
     if rank == 0:
         peak, peak_kind = measured_peak()
         fwd_gbs = work["fwd_bytes"] / (fwd_ms * 1e-3) / 1e9
         bwd_gbs = work["bwd_bytes"] / (bwd_ms * 1e-3) / 1e9
         dom = "forward" if fwd_ms >= bwd_ms else "backward"
-        ach = fwd_gbs if dom == "forward" else bwd_gbs
+        kname = kernel_name(args, dom)
+        dom_ms = fwd_ms if dom == "forward" else bwd_ms
+        dom_bytes = work["fwd_bytes"] if dom == "forward" else work["bwd_bytes"]
+        dom_flops = (8.0 if dom == "forward" else 16.0) * work["macs"]   # 8 flops per complex MAC and product
         flops = 24.0 * work["macs"]
+        # both roofs of the dominant kernel; the binding one is the slower
+        hbm_ms = dom_bytes / (peak * 1e9) * 1e3
+        fp32_ms = dom_flops / (fp32_peak * 1e12) * 1e3 if fp32_peak > 0 else None
+        fp32_binds = fp32_ms is not None and fp32_ms > hbm_ms
+        tr = TRAFFIC_RATIO.get(kname) if args.workload == "cfg3" else None
+        roof = {"bound": "fp32" if fp32_binds else "hbm", "kernel": kname}
+        if fp32_binds:
+            ach = dom_flops / (dom_ms * 1e-3) / 1e12
+            roof.update({"achieved": ach, "peak": fp32_peak, "unit": "TFLOP/s", "frac": ach / fp32_peak,
+                         "peak_kind": "measured in this run (FFMA probe kernel)"})
+        else:
+            ach = dom_bytes / (dom_ms * 1e-3) / 1e9
+            roof.update({"achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": peak_kind})
+        roof.update({
+            "traffic": tr[0] * dom_bytes if tr else None,
+            "traffic_source": ("%s of %s" % (tr[1], kname)) if tr else None,
+            "algorithmic_bytes_per_launch": dom_bytes, "algorithmic_flops_per_launch": dom_flops,
+            "hbm_ms": hbm_ms, "fp32_ms": fp32_ms, "hbm_peak_gbs": peak, "hbm_peak_kind": peak_kind,
+            "fp32_peak_tflops": fp32_peak, "hbm_frac": dom_bytes / (dom_ms * 1e-3) / 1e9 / peak,
+            "fwd": {"ms": fwd_ms, "GBps": fwd_gbs, "frac": fwd_gbs / peak},
+            "bwd": {"ms": bwd_ms, "GBps": bwd_gbs, "frac": bwd_gbs / peak},
+            "fwd_bwd_frac_of_hbm_roofline": (work["fwd_bytes"] + work["bwd_bytes"]) / 1e9 / peak / (tot_ms * 1e-3),
+            "fp32_tflops": flops / (tot_ms * 1e-3) / 1e12})
         out = {
             "metric": "cg_product_fwd_bwd_ms_per_call", "value": tot_ms, "unit": "ms", "n_gpus": world, "steps": K,
-            "warmup": args.warmup, "ms_per_step": tot_ms, "higher_is_better": False, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": tot_ms, "higher_is_better": False,
+            "scaling": "strong" if strong else "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "%s: %s; per-GPU batch %d, global batch %d" % (args.workload, desc, B, B * world),
                        "l2": "operands larger than L2 (output and upstream gradient %.1f GB each per GPU)"
                              % (work["fwd_bytes"] / 1e9),
                        "parallelism": "batch sharded over %d GPU(s), no collective on the data path" % world,
                        "fwd_kernel": args.fwd_kernel, "bwd_kernel": args.bwd_kernel},
-            "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+            "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "stages_ms": stage_ms,
             "cells_per_s": B * world / (tot_ms * 1e-3),
-            "roofline": {"bound": "hbm", "kernel": kernel_name(args, dom),
-                         "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": peak_kind,
-                         "traffic": (TRAFFIC_RATIO[(args.workload, dom)] * (work["fwd_bytes"] if dom == "forward" else work["bwd_bytes"])
-                                     if (args.workload, dom) in TRAFFIC_RATIO else None),
-                         "algorithmic_bytes_per_launch": work["fwd_bytes"] if dom == "forward" else work["bwd_bytes"],
-                         "fwd": {"ms": fwd_ms, "GBps": fwd_gbs, "frac": fwd_gbs / peak},
-                         "bwd": {"ms": bwd_ms, "GBps": bwd_gbs, "frac": bwd_gbs / peak},
-                         "fwd_bwd_frac_of_hbm_roofline": (work["fwd_bytes"] + work["bwd_bytes"]) / 1e9 / peak / (tot_ms * 1e-3),
-                         "fp32_tflops": flops / (tot_ms * 1e-3) / 1e12},
+            "roofline": roof,
             "gpu_launches": launches,
             "clocks": clocks,
             "wall_ms_per_step": t_wall * 1e3 / K,
         }
+        if strong_ms is not None:
+            out["strong_scaling"] = {"global_batch": B, "ms_per_step": strong_ms,
+                                     "efficiency": tot_ms / (world * strong_ms),
+                                     "note": "fixed global batch %d split over %d ranks; efficiency = t(1 GPU, this run's "
+                                             "per-rank weak step) / (N x t_N)" % (B, world)}
         if e2e_ms is not None:
             out["e2e"] = {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
         if world == 1 and not args.no_cpu_baseline:

@@ -65,6 +65,7 @@ SYMBOLS = {
     "gelib_kernel_launch_count": (ctypes.c_longlong, []),
     "gelib_set_option": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_char_p]),
     "gelib_async_status": (ctypes.c_int, []),
+    "gelib_probe_fp32_tflops": (ctypes.c_double, [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
 }
 
 

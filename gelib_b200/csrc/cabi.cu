@@ -442,6 +442,10 @@ int gelib_set_option(const char* name, const char* value) {
   return GELIB_OK;
 }
 
+double gelib_probe_fp32_tflops(float* scratch, int ctas, int reps, void* stream) {
+  return probe_fp32_tflops(scratch, ctas, reps, (cudaStream_t)stream);
+}
+
 int gelib_async_status(void) { return poll_async_status("gelib_async_status"); }
 
 }  // extern "C"

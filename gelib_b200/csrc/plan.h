@@ -63,6 +63,7 @@ enum { kStatusFwdTc = 0, kStatusBwdTc = 1, kStatusBwdPair = 2, kStatusCount = 3 
 int* async_status_word(int which);        // nullptr when the mapped allocation failed
 int poll_async_status(const char* fn);    // GELIB_OK, or GELIB_CUDA_ERROR with the message set (words cleared)
 
+double probe_fp32_tflops(float* scratch, int ctas, int reps, cudaStream_t s);  // measured FFMA rate, probe.cu
 bool device_has_tcgen05();  // compute capability 10.x on the current device (cached per device)
 long long launch_count();
 const std::string& last_error();

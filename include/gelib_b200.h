@@ -177,6 +177,12 @@ int gelib_SO3vec_addSPharm(int nr, const gelib_tensor5* r, const gelib_tensor5* 
 /* Number of kernels this library has launched in the calling process (all threads, all devices). */
 long long gelib_kernel_launch_count(void);
 
+/* Measured FP32 multiply-add rate of the current device in TFLOP/s (2 flops per FFMA; best of `reps` launches of a
+ * kernel of independent FFMA chains on `ctas` CTAs of 256 threads), the second roof of these kernels beside HBM
+ * bandwidth.  `scratch`: ctas*256 floats of the caller's device memory.  <= 0 on failure.  The reference has no
+ * counterpart (its benchmark, benchmarking/benchmark_CGproduct.cpp:70-92, reports a CPU op rate). */
+double gelib_probe_fp32_tflops(float* scratch, int ctas, int reps, void* stream);
+
 /* Kernel selection and test switches.  The reference chooses between its kernels inside the launcher
  * (cuda/SO3part_addCGproduct.cu:226-262: tiled or not, coefficients preloaded or not) with no way to steer it;
  * here the choice can be pinned.  name "fwd": "auto" | "simt" | "tcgen05" | "tcgen05!";  name "bwd": "auto" |
