@@ -14,11 +14,53 @@ from .SO3element import SO3element
 from .SO3irrep import SO3irrep
 
 
+class _ApplyFn(torch.autograd.Function):
+    """x -> D x on the device (gelib_SO3part_apply); the gradient is D^H g."""
+
+    @staticmethod
+    def forward(ctx, x, D):
+        ctx.save_for_backward(D)
+        xd = x.detach().as_subclass(torch.Tensor)
+        r = torch.empty_like(xd)
+        gb.SO3part.view(r).add_apply(gb.SO3part.view(xd), D, overwrite=True)
+        return r
+
+    @staticmethod
+    def backward(ctx, g):
+        (D,) = ctx.saved_tensors
+        gd = g.as_subclass(torch.Tensor).contiguous()
+        xg = torch.empty_like(gd)
+        gb.SO3part.view(xg).add_apply(gb.SO3part.view(gd), D.conj().t().contiguous(), overwrite=True)
+        return xg, None
+
+
 def _apply_rotation(t, R, cls):
     assert isinstance(R, SO3element)
     l = (t.size(-2) - 1) // 2
     D = SO3irrep(l).matrix(R).to(t.device)
-    return cls(torch.matmul(D, t))
+    if not t.is_cuda:  # host helper for tests on CPU tensors, as in the reference (python/src/gelib/SO3part.py:132-135)
+        return cls(torch.matmul(D, t))
+    return cls(_ApplyFn.apply(t, D))
+
+
+class SO3partArr_GatherFn(torch.autograd.Function):
+    """python/src/gelib/SO3partArr.py:240-256."""
+
+    @staticmethod
+    def forward(ctx, x, gmap, d):
+        ctx.gmap, ctx.d = gmap, d
+        ctx.xshape = list(x.shape)
+        shape = list(x.shape)
+        shape[d + 1] = gmap.d_out()
+        r = torch.zeros(shape, dtype=torch.complex64, device=x.device)
+        gb.SO3part.view(r).add_gather(x.detach().as_subclass(torch.Tensor).contiguous(), gmap, d)
+        return r.as_subclass(SO3partArr)
+
+    @staticmethod
+    def backward(ctx, rg):
+        xg = torch.zeros(ctx.xshape, dtype=torch.complex64, device=rg.device)
+        gb.SO3part.view(xg).add_gather_back(rg.as_subclass(torch.Tensor).contiguous(), ctx.gmap, ctx.d)
+        return xg, None, None
 
 
 def _odot(x, y):
@@ -276,6 +318,11 @@ class SO3partArr(torch.Tensor):
 
     def apply(self, R):
         return _apply_rotation(self, R, SO3partArr)
+
+    def gather(self, gmap, dim=0):
+        """Sums the cells of array dimension `dim` into new cells as the gather_map says
+        (python/src/gelib/SO3partArr.py:142-146)."""
+        return SO3partArr_GatherFn.apply(self, gmap, dim)
 
     def CGproduct(self, y, l):
         assert isinstance(y, SO3partArr)

@@ -247,6 +247,10 @@ class SO3vecArr(_VecBase):
         p = self.parts[min(self.parts)]
         return list(p.size()[1:p.dim() - 2])
 
+    def gather(self, gmap, dim=0):
+        """python/src/gelib/SO3vecArr.py:230-234: every part is gathered with the same map."""
+        return SO3vecArr(*[SO3partArr(p).gather(gmap, dim) for p in self.parts.values()])
+
 
 def MakeZeroSO3parts(b, tau, device):
     """python/src/gelib/SO3vec.py:531-536."""

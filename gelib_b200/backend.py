@@ -88,6 +88,105 @@ def CGproduct(x, y, maxl=-1):
     return x.CGproduct(y, maxl)
 
 
+class gather_map:
+    """``gelib_base.gather_map`` (python/bindings/gather_map_py.cpp:15-29): which cells of an array dimension are summed
+    into which.  cnine's GatherMapB is not part of the reference tree, so the three constructors are restated from
+    their published signatures: ``sources_targets`` pairs up two index lists (source i feeds target i),
+    ``from_matrix`` reads an (n_out, n_in) matrix whose non-zero entries mark (target, source) pairs, ``random`` draws
+    every (target, source) pair with probability p.  Held as CSR (targets -> sources) and its transpose, as int32
+    tensors that follow the operand's device."""
+
+    def __init__(self, n_in, n_out, targets, sources):
+        self.n_in, self.n_out = int(n_in), int(n_out)
+        t = torch.as_tensor(targets, dtype=torch.int64).reshape(-1)
+        s = torch.as_tensor(sources, dtype=torch.int64).reshape(-1)
+        assert t.numel() == s.numel()
+        if t.numel():
+            assert int(t.min()) >= 0 and int(t.max()) < self.n_out and int(s.min()) >= 0 and int(s.max()) < self.n_in
+        self._fwd = self._csr(t, s, self.n_out)
+        self._bwd = self._csr(s, t, self.n_in)
+        self._dev = {}
+
+    @staticmethod
+    def _csr(rows, cols, nrows):
+        order = torch.argsort(rows, stable=True)
+        counts = torch.bincount(rows, minlength=nrows)
+        ptr = torch.zeros(nrows + 1, dtype=torch.int64)
+        ptr[1:] = torch.cumsum(counts, 0)
+        return ptr.to(torch.int32), cols[order].to(torch.int32)
+
+    @classmethod
+    def sources_targets(cls, sources, targets, n_in=None, n_out=None):
+        n_in = (max(sources) + 1 if len(sources) else 0) if n_in is None else n_in
+        n_out = (max(targets) + 1 if len(targets) else 0) if n_out is None else n_out
+        return cls(n_in, n_out, targets, sources)
+
+    @classmethod
+    def from_matrix(cls, M, n_in, n_out):
+        M = torch.as_tensor(M)
+        assert list(M.shape) == [n_out, n_in]
+        idx = torch.nonzero(M.cpu())
+        return cls(n_in, n_out, idx[:, 0], idx[:, 1])
+
+    @classmethod
+    def random(cls, n, m, p=0.5, generator=None):
+        return cls.from_matrix(torch.rand(m, n, generator=generator) < p, n, m)
+
+    def d_in(self):
+        return self.n_in
+
+    def d_out(self):
+        return self.n_out
+
+    def csr(self, device, transposed=False):
+        key = (str(device), transposed)
+        if key not in self._dev:
+            ptr, col = self._bwd if transposed else self._fwd
+            if col.numel() == 0:
+                col = torch.zeros(1, dtype=torch.int32)
+            self._dev[key] = (ptr.to(device), col.to(device))
+        return self._dev[key]
+
+    def __repr__(self):
+        return "<GElib::gather_map(n_in=%d,n_out=%d,pairs=%d)>" % (self.n_in, self.n_out, int(self._fwd[0][-1]))
+
+    def str(self, indent=""):
+        ptr, col = self._fwd
+        return "\n".join("%s%d<-(%s)" % (indent, t, ",".join(str(int(c)) for c in col[ptr[t]:ptr[t + 1]]))
+                         for t in range(self.n_out) if ptr[t + 1] > ptr[t])
+
+    __str__ = str
+
+
+def _gather(r, x, gmap, d, transposed):
+    """r[.., t, ..] += sum of x[.., s, ..] along array dimension d (tensor dimension d + 1)."""
+    _one_device(r, x)
+    if not r.is_cuda:
+        raise RuntimeError("gelib_b200: tensors must live on a CUDA device (there is no CPU path).")
+    if not (r.is_contiguous() and x.is_contiguous()):
+        raise RuntimeError("GElib error: add_gather needs contiguous tensors.")
+    n_out, n_in = (gmap.n_in, gmap.n_out) if transposed else (gmap.n_out, gmap.n_in)
+    if r.size(d + 1) != n_out or x.size(d + 1) != n_in:
+        raise RuntimeError("GElib error: gather map does not match the array dimension.")
+    outer = 1
+    for k in range(d + 1):
+        outer *= r.size(k)
+    inner = 1
+    for k in range(d + 2, r.dim()):
+        inner *= r.size(k)
+    ptr, col = gmap.csr(r.device, transposed)
+    with device_guard(r):
+        return check(lib().gelib_add_gather(r.data_ptr(), x.data_ptr(), outer, n_out, n_in, inner, ptr.data_ptr(),
+                                            col.data_ptr(), stream_of(r)))
+
+
+def SO3irrep_matrix(l, alpha, beta, gamma):
+    """D^l(alpha, beta, gamma) as a (2l+1, 2l+1) complex64 CPU tensor (SO3irrep::matrix, SO3/SO3irrep.hpp:69-103)."""
+    out = torch.zeros(2 * l + 1, 2 * l + 1, dtype=torch.complex64)
+    check(lib().gelib_SO3irrep_matrix(l, float(alpha), float(beta), float(gamma), out.data_ptr()))
+    return out
+
+
 class SO3part:
     """Zero-copy view of a complex64 tensor (batch, [grid...], 2l+1, channels)."""
 
@@ -144,6 +243,23 @@ class SO3part:
     @staticmethod
     def add_DiagCGproduct_back01(xg, yg, g, x, y, offs=0):
         return SO3part._back01("gelib_SO3part_addDiagCGproduct_back01", xg, yg, g, x, y, offs)
+
+    def add_gather(self, x, gmap, d=0):
+        """python/bindings/SO3part_py.cpp:21-22."""
+        return _gather(self.t, x.t if isinstance(x, SO3part) else x, gmap, d, False)
+
+    def add_gather_back(self, rg, gmap, d=0):
+        """python/bindings/SO3part_py.cpp:23-24: the gradient of add_gather (the transposed map)."""
+        return _gather(self.t, rg.t if isinstance(rg, SO3part) else rg, gmap, d, True)
+
+    def add_apply(self, x, D, *, overwrite=False):
+        """self (+)= D x cell by cell; D a (2l+1, 2l+1) complex64 tensor on the same device."""
+        _one_device(self.t, x.t, D)
+        with device_guard(self.t):
+            dr, dx = descriptor(self.t), descriptor(x.t)
+            Dc = D.contiguous()
+            return check(lib().gelib_SO3part_apply(ctypes.byref(dr), ctypes.byref(dx), Dc.data_ptr(),
+                                                   GELIB_OVERWRITE if overwrite else 0, stream_of(self.t)))
 
     def add_spharm(self, X, *, overwrite=False):
         """self += Y_l(X) for X (batch, [grid...], 3, channels) float32, or (3, channels) broadcast over the batch."""

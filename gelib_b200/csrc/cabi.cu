@@ -434,6 +434,41 @@ int gelib_SO3part_addSPharm(const gelib_tensor5* r, const gelib_tensor5* x, int 
   return gelib_SO3vec_addSPharm(1, r, x, flags, stream);
 }
 
+// ---- callers of the path: gather over an array dimension, Wigner-D apply --------------------------------------
+
+int gelib_add_gather(float* r, const float* x, long long outer, int n_out, int n_in, long long inner, const int* row_ptr,
+                     const int* col, void* stream) {
+  static const char* fn = "add_gather";
+  if (outer < 0 || n_out < 0 || n_in < 0 || inner < 0) return fail(GELIB_INVALID, fn, "negative size");
+  if ((outer && n_out && inner) && (!r || !x || !row_ptr || !col)) return fail(GELIB_INVALID, fn, "null pointer");
+  return launch_gather(r, x, outer, n_out, n_in, inner, row_ptr, col, (cudaStream_t)stream);
+}
+
+int gelib_SO3irrep_matrix(int l, double alpha, double beta, double gamma, float* out) {
+  if (l < 0 || !out) return fail(GELIB_INVALID, "SO3irrep_matrix", "negative l or null output");
+  wigner_D(l, alpha, beta, gamma, out);
+  return GELIB_OK;
+}
+
+int gelib_SO3part_apply(const gelib_tensor5* r, const gelib_tensor5* x, const float* D, int flags, void* stream) {
+  static const char* fn = "SO3part_apply";
+  VecCall c;
+  std::vector<const gelib_tensor5*> sr, sx;
+  std::vector<PartView> xv;
+  int st;
+  if (!D) return fail(GELIB_INVALID, fn, "null matrix");
+  if ((st = parse_parts(fn, "r", 1, r, false, &c.r, &sr)) != GELIB_OK) return st;
+  if ((st = parse_parts(fn, "x", 1, x, false, &xv, &sx)) != GELIB_OK) return st;
+  if (c.r[0].l != xv[0].l || c.r[0].n != xv[0].n) return fail(GELIB_INVALID, fn, "r does not have the shape of x");
+  std::vector<Group> groups;
+  bool rb = false, xb = false;
+  groups.push_back({&c.r, &sr, &rb});
+  groups.push_back({&xv, &sx, &xb});
+  if ((st = reconcile(fn, groups, &c.cg)) != GELIB_OK) return st;
+  if (rb) return fail(GELIB_SKIPPED, fn, "r is broadcast over the batch");
+  return launch_apply(c.r[0], xv[0], c.cg, D, flags, (cudaStream_t)stream);
+}
+
 long long gelib_kernel_launch_count(void) { return launch_count(); }
 
 int gelib_set_option(const char* name, const char* value) {

@@ -45,6 +45,10 @@ int launch_diag_bwd_fast(const VecCall& c, cudaStream_t s);  // -1 when the call
 // Work items of a diagonal product (defined in diag.cu): {first triple | nl<<16, m, coefficient offset, padded nl}
 void build_diag_items(DevicePlan& p, const std::vector<PartSig>& xs, const std::vector<PartSig>& ys,
                       const std::vector<PartSig>& rs, int* max_nl);
+int launch_gather(float* r, const float* x, long long outer, int n_out, int n_in, long long inner, const int* row_ptr,
+                  const int* col, cudaStream_t s);
+int launch_apply(const PartView& r, const PartView& x, const CellGrid& cg, const float* D, int flags, cudaStream_t s);
+void wigner_D(int l, double alpha, double beta, double gamma, float* out);
 int launch_spharm(const std::vector<PartView>& r, const PartView& x, const CellGrid& cg, int flags, cudaStream_t s);
 
 // Kernel selection and debug switches.  Initial values come from the environment (GELIB_B200_FWD, GELIB_B200_BWD,

@@ -172,6 +172,25 @@ int gelib_SO3vec_addCGproduct_static(int nr, const gelib_tensor5* r, int nx, con
  * SO3part.spharm writes, python/src/gelib/SO3part.py:54-62). */
 int gelib_SO3vec_addSPharm(int nr, const gelib_tensor5* r, const gelib_tensor5* x, int flags, void* stream);
 
+/* ---- callers of the path ------------------------------------------------------------------------ */
+
+/* Gather along one array dimension of an SO3partArr (message passing): for every outer index o and target t,
+ *   r[o][t][:] += sum over k in [row_ptr[t], row_ptr[t+1]) of x[o][col[k]][:]
+ * with r (outer, n_out, inner) and x (outer, n_in, inner) dense complex64 tensors and the map as CSR in device memory.
+ * Replaces Gpart::add_gather (core/Gpart.hpp:555-557, via cnine::GatherSlices); add_gather_back (core/Gpart.hpp:559-561)
+ * is the same call with the transposed map. */
+int gelib_add_gather(float* r, const float* x, long long outer, int n_out, int n_in, long long inner, const int* row_ptr,
+                     const int* col, void* stream);
+
+/* Wigner matrix D^l of the rotation with z-y-z Euler angles (alpha, beta, gamma), as SO3irrep::matrix builds it
+ * (SO3/SO3irrep.hpp:69-103): out[(m1+l)*(2l+1) + (m2+l)] = d^l_{m2 m1}(beta) e^{i m1 alpha} e^{i m2 gamma}, interleaved
+ * (re, im) floats, host memory. */
+int gelib_SO3irrep_matrix(int l, double alpha, double beta, double gamma, float* out);
+
+/* r[cell] (+)= D x[cell] for every cell: the rotation of an SO3part (SO3part.apply, python/src/gelib/SO3part.py:132-135,
+ * which multiplies by the host-built matrix with torch.matmul).  D: (2l+1)^2 complex64 in DEVICE memory, row-major. */
+int gelib_SO3part_apply(const gelib_tensor5* r, const gelib_tensor5* x, const float* D, int flags, void* stream);
+
 /* ---- introspection ------------------------------------------------------------------------------- */
 
 /* Number of kernels this library has launched in the calling process (all threads, all devices). */

@@ -1,0 +1,128 @@
+"""Callers of the Clebsch-Gordan path on device: gather over an array dimension, the Wigner-D apply, O(3) parts and
+vectors (parity bookkeeping over the SO(3) kernels)."""
+import numpy as np
+import pytest
+import torch
+
+from util import crandn, np_c, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def G():
+    import gelib_b200
+    assert torch.cuda.is_available()
+    gelib_b200._lib.lib()
+    return gelib_b200
+
+
+def test_gather_sums_sources_into_targets_and_backpropagates(G):
+    # core/Gpart.hpp:537-561: r = x.gather(map, d); the gradient runs through the transposed map
+    torch.manual_seed(1)
+    B, A0, A1, l, n = 2, 5, 3, 2, 4
+    x = G.SO3partArr.randn(B, [A0, A1], l, n, device="cuda")
+    sources, targets = [0, 1, 1, 4, 2, 2, 3], [3, 0, 3, 3, 1, 5, 5]
+    gm = G.gather_map.sources_targets(sources, targets, n_in=A0, n_out=7)
+    x.requires_grad_()
+    r = G.gather(x, gm, 0)
+    assert isinstance(r, G.SO3partArr) and list(r.shape) == [B, 7, A1, 5, n]
+    want = torch.zeros_like(r.detach().as_subclass(torch.Tensor))
+    want.index_add_(1, torch.tensor(targets, device="cuda"), x.detach().as_subclass(torch.Tensor)[:, sources])
+    assert rel_err(r, want) < 1e-6
+    assert float(r[:, 2].abs().max()) == 0.0 and float(r[:, 4].abs().max()) == 0.0 and float(r[:, 6].abs().max()) == 0.0
+    g = torch.randn_like(want)
+    r.backward(g)
+    gw = torch.zeros_like(x.detach().as_subclass(torch.Tensor))
+    gw.index_add_(1, torch.tensor(sources, device="cuda"), g[:, targets])
+    assert rel_err(x.grad, gw) < 1e-6
+    # along the second array dimension, and a map given as a matrix
+    M = (torch.rand(4, A1, generator=torch.Generator().manual_seed(2)) < 0.6)
+    gm2 = G.gather_map.from_matrix(M, A1, 4)
+    r2 = x.detach().gather(gm2, 1)
+    want2 = torch.einsum("ts,bastn->batn".replace("stn", "sxn").replace("batn", "batxn").replace("bastn", "basxn"),
+                         M.to(torch.complex64).cuda(), x.detach().as_subclass(torch.Tensor))
+    assert rel_err(r2, want2) < 1e-6
+    v = G.SO3vecArr.randn(B, [A0], {0: 2, 1: 3}, device="cuda")
+    w = v.gather(gm, 0)
+    assert list(w.parts[1].shape) == [B, 7, 3, 3]
+
+
+@pytest.mark.parametrize("l", [0, 1, 3, 6])
+def test_wigner_matrix_and_device_apply(G, l):
+    # D from the C ABI equals the Python restatement of SO3/SO3irrep.hpp:69-103; apply = D x cell by cell; D is unitary
+    R = G.SO3element.random(torch.Generator().manual_seed(l))
+    from gelib_b200.SO3irrep import euler_zyz
+    a, b, c = euler_zyz(R.numpy())
+    D1 = G.backend.SO3irrep_matrix(l, a, b, c)
+    D2 = G.SO3irrep(l).matrix(R)
+    assert rel_err(D1, D2) < 1e-6
+    assert rel_err(D1 @ D1.conj().t(), torch.eye(2 * l + 1, dtype=torch.complex64)) < 1e-5
+    x = G.SO3part.randn(3, l, 5, device="cuda")
+    x.requires_grad_()
+    y = x.apply(R)
+    assert rel_err(y, torch.matmul(D2.cuda(), x.detach().as_subclass(torch.Tensor))) < 1e-6
+    g = torch.randn_like(y.detach().as_subclass(torch.Tensor))
+    y.backward(g)
+    assert rel_err(x.grad, torch.matmul(D2.cuda().conj().t(), g)) < 1e-6
+    arr = G.SO3partArr.randn(2, [3], l, 4, device="cuda")
+    assert rel_err(arr.apply(R), torch.matmul(D2.cuda(), arr.as_subclass(torch.Tensor))) < 1e-6
+
+
+def test_o3_vector_product_matches_the_reference_loop(G, oracle):
+    """O3vec.CGproduct against a direct restatement of the reference's loop (core/Gvec.hpp:311-321 with O(3) indices):
+    parts in index order 2l + [p = -1], (l1,p1) x (l2,p2) feeds (l, p1 p2), offsets advance by n1 n2 per triple."""
+    torch.manual_seed(4)
+    B, maxl = 3, 3
+    tx = {(0, 1): 2, (1, -1): 3, (1, 1): 1, (2, 1): 2}
+    ty = {(0, -1): 2, (1, 1): 2, (2, -1): 1, (2, 1): 3}
+    x, y = G.O3vec.randn(B, tx, device="cuda"), G.O3vec.randn(B, ty, device="cuda")
+    assert list(x.parts) == [(0, 1), (1, 1), (1, -1), (2, 1)]
+    x.requires_grad_()
+    y.requires_grad_()
+    z = x.CGproduct(y, maxl)
+    rtype = G.O3type(tx).CGproduct(G.O3type(ty), maxl).get_parts()
+    assert z.tau() == rtype
+    want = {mu: np.zeros((B, 2 * mu[0] + 1, n), np.complex64) for mu, n in rtype.items()}
+    offs = {mu: 0 for mu in rtype}
+    for (l1, p1), xp in x.parts.items():
+        for (l2, p2), yp in y.parts.items():
+            for l in range(abs(l1 - l2), min(l1 + l2, maxl) + 1):
+                mu = (l, p1 * p2)
+                oracle.add_CGproduct(want[mu], np_c(xp.as_subclass(torch.Tensor)), np_c(yp.as_subclass(torch.Tensor)), offs=offs[mu])
+                offs[mu] += xp.size(-1) * yp.size(-1)
+    for mu, w in want.items():
+        assert rel_err(z.parts[mu], w) < 1e-5, mu
+    # gradients: first-order check as in python/tests/ci_tests/test_SO3vec.py:83-105
+    tv = G.O3vec.randn_like(z)
+    loss = z.odot(tv)
+    loss.backward()
+    xeps = G.O3vec.randn_like(x)
+    xloss = (x + xeps).CGproduct(y, maxl).odot(tv)
+    assert torch.allclose(xloss - loss, xeps.odot(x.get_grad()), rtol=1e-3, atol=1e-2)
+    yeps = G.O3vec.randn_like(y)
+    yloss = x.CGproduct(y + yeps, maxl).odot(tv)
+    assert torch.allclose(yloss - loss, yeps.odot(y.get_grad()), rtol=1e-3, atol=1e-2)
+
+
+@pytest.mark.parametrize("diag", [False, True])
+def test_o3_products_are_equivariant_under_improper_rotations(G, diag):
+    torch.manual_seed(6)
+    gen = torch.Generator().manual_seed(8)
+    R = G.O3element(-G.SO3element.random(gen).as_subclass(torch.Tensor))   # determinant -1
+    assert R.parity() == -1
+    tau = {(0, 1): 2, (1, -1): 2, (1, 1): 2, (2, -1): 2}
+    x, y = G.O3vec.randn(2, tau, device="cuda"), G.O3vec.randn(2, tau, device="cuda")
+    f = (lambda a, c: a.DiagCGproduct(c, 2)) if diag else (lambda a, c: a.CGproduct(c, 2))
+    z, zr = f(x, y).apply(R), f(x.apply(R), y.apply(R))
+    for mu in z.parts:
+        assert torch.allclose(z.parts[mu].as_subclass(torch.Tensor), zr.parts[mu].as_subclass(torch.Tensor), rtol=1e-3, atol=1e-4), mu
+    # parts: the parity rule is enforced, spherical harmonics carry (-1)^l
+    a, c = G.O3part.randn(2, (1, -1), 3, device="cuda"), G.O3part.randn(2, (2, -1), 3, device="cuda")
+    w = a.CGproduct(c, (2, 1))
+    assert w.mu == (2, 1) and list(w.shape) == [2, 5, 9]
+    with pytest.raises(AssertionError):
+        a.CGproduct(c, (2, -1))
+    X = torch.randn(4, 3, 2, device="cuda")
+    s = G.O3part.spharm(3, X)
+    assert s.mu == (3, -1) and rel_err(G.O3part.spharm(3, -X), -s) < 1e-5
