@@ -37,14 +37,21 @@ def _vec_forward(ctx, k1, k2, maxl, args, diag, part_cls):
 def _vec_backward(ctx, gargs):
     k1, k2 = ctx.k1, ctx.k2
     saved = ctx.saved_tensors
-    grads = [torch.zeros_like(t) for t in saved]
+    need = ctx.needs_input_grad[3:]
+    need_x, need_y = any(need[0:k1]), any(need[k1:k1 + k2])
+    # a side that needs no gradient (spherical harmonics of fixed points, say) is not computed at all
+    grads = [torch.zeros_like(t) if (need_x if i < k1 else need_y) else None for i, t in enumerate(saved)]
     x, y = gb.SO3vec.view(list(saved[0:k1])), gb.SO3vec.view(list(saved[k1:k1 + k2]))
     g = gb.SO3vec.view([a.as_subclass(torch.Tensor) for a in gargs])
-    xg, yg = gb.SO3vec.view(grads[0:k1]), gb.SO3vec.view(grads[k1:k1 + k2])
-    if ctx.diag:
-        gb.SO3vec.addDiagCGproduct_back01(xg, yg, g, x, y)
-    else:
-        gb.SO3vec.addCGproduct_back01(xg, yg, g, x, y)
+    if need_x and need_y:
+        xg, yg = gb.SO3vec.view(grads[0:k1]), gb.SO3vec.view(grads[k1:k1 + k2])
+        (gb.SO3vec.addDiagCGproduct_back01 if ctx.diag else gb.SO3vec.addCGproduct_back01)(xg, yg, g, x, y)
+    elif need_x:
+        xg = gb.SO3vec.view(grads[0:k1])
+        (xg.addDiagCGproduct_back0 if ctx.diag else xg.addCGproduct_back0)(g, y)
+    elif need_y:
+        yg = gb.SO3vec.view(grads[k1:k1 + k2])
+        (yg.addDiagCGproduct_back1 if ctx.diag else yg.addCGproduct_back1)(g, x)
     return tuple([None, None, None] + grads)
 
 
