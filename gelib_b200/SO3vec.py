@@ -103,6 +103,35 @@ class SO3vecArr_DiagCGproductFn(torch.autograd.Function):
         return _vec_backward(ctx, args)
 
 
+class SO3vec_SpharmCGproductFn(torch.autograd.Function):
+    """CGproduct(spharms(lmax_x, X), y, maxl) as one fused call per direction: the harmonics are generated inside the
+    kernels and never reach memory (the first layer of a network on point clouds: SO3/SO3part.hpp:150-156, 340-397
+    followed by core/Gvec.hpp:311-321).  X carries no gradient."""
+
+    @staticmethod
+    def forward(ctx, X, lmax_x, maxl, *yparts):
+        ys = [a.detach() for a in yparts]
+        ctx.lmax_x = lmax_x
+        ctx.save_for_backward(X, *yparts)
+        tx = gb.SO3type({l: 1 for l in range(lmax_x + 1)})
+        y = gb.SO3vec.view(ys)
+        tau = tx.CGproduct(y.get_tau(), maxl)
+        rparts = [torch.empty([X.size(0), 2 * l + 1, n], dtype=torch.complex64, device=X.device)
+                  for l, n in tau.get_parts().items()]
+        if not gb.SO3vec.view(rparts).addCGproduct_spharm(X, lmax_x, y, overwrite=True):
+            for p in rparts:
+                p.zero_()
+        return tuple(p.as_subclass(SO3part) for p in rparts)
+
+    @staticmethod
+    def backward(ctx, *gargs):
+        X = ctx.saved_tensors[0]
+        grads = [torch.zeros_like(t) for t in ctx.saved_tensors[1:]]
+        g = gb.SO3vec.view([a.as_subclass(torch.Tensor).contiguous() for a in gargs])
+        gb.SO3vec.view(grads).addCGproduct_spharm_back1(g, X, ctx.lmax_x)
+        return tuple([None, None, None] + grads)
+
+
 class _VecBase:
     """What SO3vec and SO3vecArr share: a dict l -> part tensor."""
     _part = SO3part
@@ -217,6 +246,12 @@ class SO3vec(_VecBase):
         """The SO3vec whose only part is Y_l(X), X (b, 3, n) float32."""
         assert X.dim() == 3
         return SO3vec(SO3part.spharm(l, X))
+
+    @classmethod
+    def spharm_CGproduct(cls, lmax_x, X, y, maxl=-1):
+        """CGproduct(SO3vec.spharms(lmax_x, X), y, maxl) without materialising the harmonics; X (b, 3, 1) float32."""
+        assert X.dim() == 3 and X.size(1) == 3 and X.size(2) == 1
+        return SO3vec(*SO3vec_SpharmCGproductFn.apply(X, lmax_x, maxl, *list(y.parts.values())))
 
     @classmethod
     def spharms(cls, maxl, X):

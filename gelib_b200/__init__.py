@@ -13,7 +13,7 @@ from .SO3irrep import SO3irrep
 from .SO3type import SO3type
 from .SO3part import (SO3part, SO3partArr, SO3part_CGproductFn, SO3part_DiagCGproductFn, SO3partArr_CGproductFn,
                       SO3partArr_DiagCGproductFn)
-from .SO3vec import (SO3vec, SO3vecArr, SO3vec_CGproductFn, SO3vec_DiagCGproductFn, SO3vecArr_CGproductFn,
+from .SO3vec import (SO3vec, SO3vecArr, SO3vec_SpharmCGproductFn, SO3vec_CGproductFn, SO3vec_DiagCGproductFn, SO3vecArr_CGproductFn,
                      SO3vecArr_DiagCGproductFn, MakeZeroSO3parts, MakeZeroSO3partArrs)
 from .SO3weights import SO3weights, SO3linear
 from .O3 import (O3element, O3irrep, O3type, O3part, O3vec, O3part_CGproductFn, O3part_DiagCGproductFn, O3vec_CGproductFn,

@@ -62,6 +62,10 @@ SYMBOLS = {
     "gelib_SO3vec_addDiagCGproduct_back1": (ctypes.c_int, _VEC3),
     "gelib_SO3vec_addDiagCGproduct_back01": (ctypes.c_int, _VEC5),
     "gelib_SO3vec_addSPharm": (ctypes.c_int, [ctypes.c_int, _P5, _P5, ctypes.c_int, ctypes.c_void_p]),
+    "gelib_SO3vec_addCGproduct_spharm": (ctypes.c_int, [ctypes.c_int, _P5, _P5, ctypes.c_int, ctypes.c_int, _P5, ctypes.c_int,
+                                                        ctypes.c_void_p]),
+    "gelib_SO3vec_addCGproduct_spharm_back1": (ctypes.c_int, [ctypes.c_int, _P5, ctypes.c_int, _P5, _P5, ctypes.c_int,
+                                                              ctypes.c_int, ctypes.c_void_p]),
     "gelib_add_gather": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
                                         ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "gelib_SO3irrep_matrix": (ctypes.c_int, [ctypes.c_int, ctypes.c_double, ctypes.c_double, ctypes.c_double, ctypes.c_void_p]),

@@ -315,6 +315,26 @@ class SO3vec:
         array shared by all calls: do not let two such calls overlap on the GPU)."""
         return self._call3("gelib_SO3vec_addCGproduct_static", self, x, y, GELIB_OVERWRITE if overwrite else 0)
 
+    def addCGproduct_spharm(self, X, lmax_x, y, *, overwrite=False):
+        """self (+)= CGproduct(spharms(lmax_x, X), y) with the harmonics generated inside the kernel; X (batch, 3, 1)."""
+        tr, ty = self._tensors(), y._tensors()
+        _one_device(*(tr + ty + [X]))
+        with device_guard(tr[0]):
+            dx = descriptor(X, real=True)
+            return check(lib().gelib_SO3vec_addCGproduct_spharm(len(tr), descriptor_array(tr), ctypes.byref(dx), lmax_x,
+                                                                len(ty), descriptor_array(ty),
+                                                                GELIB_OVERWRITE if overwrite else 0, stream_of(tr[0])))
+
+    def addCGproduct_spharm_back1(self, g, X, lmax_x):
+        """self (the gradient of y) += C g conj(spharms(lmax_x, X))."""
+        tyg, tg = self._tensors(), g._tensors()
+        _one_device(*(tyg + tg + [X]))
+        with device_guard(tg[0]):
+            dx = descriptor(X, real=True)
+            return check(lib().gelib_SO3vec_addCGproduct_spharm_back1(len(tyg), descriptor_array(tyg), len(tg),
+                                                                      descriptor_array(tg), ctypes.byref(dx), lmax_x, 0,
+                                                                      stream_of(tg[0])))
+
     def addCGproduct_back0(self, g, y):
         return self._call3("gelib_SO3vec_addCGproduct_back0", self, g, y)
 

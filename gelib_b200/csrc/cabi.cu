@@ -134,7 +134,8 @@ int check_room(const char* fn, const std::vector<PartView>& x, const std::vector
 // mode 0: forward (out = r).  mode 1/2/3: gradient wrt x / y / both (r is g).
 int run_product(const char* fn, bool diag, int mode, int nr, const gelib_tensor5* r, int nx, const gelib_tensor5* x,
                 int ny, const gelib_tensor5* y, int nxg, const gelib_tensor5* xg, int nyg, const gelib_tensor5* yg,
-                int offs, int flags, void* stream, bool single_triple, bool no_alloc = false) {
+                int offs, int flags, void* stream, bool single_triple, bool no_alloc = false,
+                const gelib_tensor5* sph_points = nullptr, int sph_lmax = 0) {
   VecCall c;
   c.diag = diag;
   c.flags = flags;
@@ -206,6 +207,16 @@ int run_product(const char* fn, bool diag, int mode, int nr, const gelib_tensor5
 
   cudaStream_t s = (cudaStream_t)stream;
   if (no_alloc) return launch_cg_strided_static(c, s);
+  if (sph_points) {  // fused first layer: the x parts are generated from the points inside the narrow kernels
+    c.sph = sph_points->base;
+    c.sph_sb = sph_points->dims[0] > 1 ? sph_points->strides[0] : 0;
+    c.sph_sm = sph_points->strides[3];
+    c.sph_lmax = sph_lmax;
+    st = mode == 0 ? launch_cg_narrow_fwd(c, s) : launch_cg_narrow_bwd(c, s);
+    if (st == -1)
+      return fail(GELIB_INVALID, fn, "the fused spherical-harmonics product takes y parts of one channel count <= 32 with l <= 7");
+    return st;
+  }
   if (mode == 0) {
     st = -1;
     if (c.dense_channels && !c.r_bcast) {
@@ -406,6 +417,40 @@ int gelib_SO3vec_addCGproduct_static(int nr, const gelib_tensor5* r, int nx, con
                                      const gelib_tensor5* y, int flags, void* stream) {
   return run_product("SO3vec_addCGproduct_static", false, 0, nr, r, nx, x, ny, y, 0, nullptr, 0, nullptr, 0, flags, stream, false,
                      true);
+}
+
+// ---- fused first layer: r = CG(Y_0..lmax(X), y) without the harmonics ever reaching memory ------------------------
+
+namespace {
+int run_sph_product(const char* fn, int mode, int nr, const gelib_tensor5* r, const gelib_tensor5* X, int lmax_x, int ny,
+                    const gelib_tensor5* y, int flags, void* stream) {
+  if (!X || !X->base) return fail(GELIB_INVALID, fn, "null points");
+  if (lmax_x < 0 || lmax_x >= GELIB_MAX_PARTS) return fail(GELIB_SKIPPED, fn, "lmax of the harmonics out of range");
+  if (X->dims[3] != 3 || X->dims[4] != 1 || X->dims[1] != 1 || X->dims[2] != 1)
+    return fail(GELIB_SKIPPED, fn, "points must be (batch, 3, 1)");
+  // stand-in descriptors for the harmonics: right shapes, never dereferenced (the kernels generate the values)
+  gelib_tensor5 xd[GELIB_MAX_PARTS];
+  for (int l = 0; l <= lmax_x; l++) {
+    xd[l].base = reinterpret_cast<float*>(reinterpret_cast<uintptr_t>(X->base) & ~(uintptr_t)7);
+    const int dims[5] = {X->dims[0], 1, 1, 2 * l + 1, 1};
+    for (int d = 0; d < 5; d++) {
+      xd[l].dims[d] = dims[d];
+      xd[l].strides[d] = d >= 3 ? 2 : 0;  // dense in the channel, as the kernels' qualification wants
+    }
+  }
+  if (mode == 0)
+    return run_product(fn, false, 0, nr, r, lmax_x + 1, xd, ny, y, 0, nullptr, 0, nullptr, 0, flags, stream, false, false, X, lmax_x);
+  return run_product(fn, false, 2, nr, r, lmax_x + 1, xd, 0, nullptr, 0, nullptr, ny, y, 0, flags, stream, false, false, X, lmax_x);
+}
+}  // namespace
+
+int gelib_SO3vec_addCGproduct_spharm(int nr, const gelib_tensor5* r, const gelib_tensor5* X, int lmax_x, int ny,
+                                     const gelib_tensor5* y, int flags, void* stream) {
+  return run_sph_product("SO3vec_addCGproduct_spharm", 0, nr, r, X, lmax_x, ny, y, flags, stream);
+}
+int gelib_SO3vec_addCGproduct_spharm_back1(int ny, const gelib_tensor5* yg, int ng, const gelib_tensor5* g,
+                                           const gelib_tensor5* X, int lmax_x, int flags, void* stream) {
+  return run_sph_product("SO3vec_addCGproduct_spharm_back1", 2, ng, g, X, lmax_x, ny, yg, flags, stream);
 }
 
 // ---- spherical harmonics ------------------------------------------------------------------------------------

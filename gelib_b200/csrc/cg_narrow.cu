@@ -20,6 +20,7 @@
 #include <algorithm>
 
 #include "plan.h"
+#include "spharm_point.h"
 
 namespace gelib_b200 {
 
@@ -44,6 +45,10 @@ struct NarrowArgs {
   int offs_extra;
   int accumulate;
   int do_x, do_y, x_atomic, y_atomic;
+  // fused first layer: x is not read but generated, part l = the spherical harmonics Y_l of the cell's point
+  const float* sph;           // points (cell, 3) or nullptr
+  long long sph_sb, sph_sm;   // strides between cells / between coordinates, in floats
+  int sph_lmax;
 };
 
 __device__ __forceinline__ float2 cmul(float2 a, float2 b) { return make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x); }
@@ -138,14 +143,22 @@ __global__ void __launch_bounds__(256) cg_narrow_fwd_kernel(const __grid_constan
   float* xs_cell = wbase + 2 * WC * kMaxParts + (size_t)lc * A.xcell_floats;
   float* cx = wbase + 2 * WC * kMaxParts + (size_t)WC * A.xcell_floats + (size_t)lc * A.cx_floats;
   for (int p = lic; p < A.nr; p += CW) roff[p] = cell_ok ? cell_offset(A.r[p], A.cg, cell) : 0;
-  for (int i = 0; i < A.nx; i++) {
-    const PartView& xp = A.x[i];
-    const float* xb = xp.base + (cell_ok ? cell_offset(xp, A.cg, cell) : 0);
-    const int total = (2 * xp.l + 1) * xp.n;
-    for (int e = lic; e < total; e += CW) {
-      const int m = e / xp.n, ch = e - m * xp.n;
-      const float2 v = cell_ok ? __ldg(reinterpret_cast<const float2*>(xb + (long long)m * xp.sm + 2 * ch)) : make_float2(0.f, 0.f);
-      *reinterpret_cast<float2*>(xs_cell + 2 * ((A.xrow0[i] + m) * A.n1max + ch)) = v;
+  if (A.sph) {  // one lane per cell generates the harmonics of the cell's point straight into the staged rows
+    if (lic == 0) {
+      const float* pt = A.sph + (cell_ok ? cell * A.sph_sb : 0);
+      spharm_point(cell_ok ? pt[0] : 0.f, cell_ok ? pt[A.sph_sm] : 0.f, cell_ok ? pt[2 * A.sph_sm] : 1.f, A.sph_lmax, xs_cell,
+                   A.xrow0, A.n1max);
+    }
+  } else {
+    for (int i = 0; i < A.nx; i++) {
+      const PartView& xp = A.x[i];
+      const float* xb = xp.base + (cell_ok ? cell_offset(xp, A.cg, cell) : 0);
+      const int total = (2 * xp.l + 1) * xp.n;
+      for (int e = lic; e < total; e += CW) {
+        const int m = e / xp.n, ch = e - m * xp.n;
+        const float2 v = cell_ok ? __ldg(reinterpret_cast<const float2*>(xb + (long long)m * xp.sm + 2 * ch)) : make_float2(0.f, 0.f);
+        *reinterpret_cast<float2*>(xs_cell + 2 * ((A.xrow0[i] + m) * A.n1max + ch)) = v;
+      }
     }
   }
   __syncwarp();
@@ -303,14 +316,22 @@ __global__ void __launch_bounds__(256) cg_narrow_bwd_kernel(const __grid_constan
   float* cx = wbase + 2 * WC * kMaxParts + (size_t)2 * WC * A.xcell_floats + (size_t)lc * A.cx_floats;
   for (int q = lic; q < A.nr; q += CW) goff[q] = cell_ok ? cell_offset(A.r[q], A.cg, cell) : 0;
   for (int e = lic; e < A.xcell_floats; e += CW) xg_cell[e] = 0.f;
-  for (int i = 0; i < A.nx; i++) {
-    const PartView& xp = A.x[i];
-    const float* xb = xp.base + (cell_ok ? cell_offset(xp, A.cg, cell) : 0);
-    const int total = (2 * xp.l + 1) * xp.n;
-    for (int e = lic; e < total; e += CW) {
-      const int m = e / xp.n, ch = e - m * xp.n;
-      const float2 v = cell_ok ? __ldg(reinterpret_cast<const float2*>(xb + (long long)m * xp.sm + 2 * ch)) : make_float2(0.f, 0.f);
-      *reinterpret_cast<float2*>(xs_cell + 2 * ((A.xrow0[i] + m) * A.n1max + ch)) = v;
+  if (A.sph) {  // one lane per cell generates the harmonics of the cell's point straight into the staged rows
+    if (lic == 0) {
+      const float* pt = A.sph + (cell_ok ? cell * A.sph_sb : 0);
+      spharm_point(cell_ok ? pt[0] : 0.f, cell_ok ? pt[A.sph_sm] : 0.f, cell_ok ? pt[2 * A.sph_sm] : 1.f, A.sph_lmax, xs_cell,
+                   A.xrow0, A.n1max);
+    }
+  } else {
+    for (int i = 0; i < A.nx; i++) {
+      const PartView& xp = A.x[i];
+      const float* xb = xp.base + (cell_ok ? cell_offset(xp, A.cg, cell) : 0);
+      const int total = (2 * xp.l + 1) * xp.n;
+      for (int e = lic; e < total; e += CW) {
+        const int m = e / xp.n, ch = e - m * xp.n;
+        const float2 v = cell_ok ? __ldg(reinterpret_cast<const float2*>(xb + (long long)m * xp.sm + 2 * ch)) : make_float2(0.f, 0.f);
+        *reinterpret_cast<float2*>(xs_cell + 2 * ((A.xrow0[i] + m) * A.n1max + ch)) = v;
+      }
     }
   }
   __syncwarp();
@@ -419,6 +440,14 @@ bool narrow_setup(const VecCall& c, NarrowArgs& a) {
   a.do_y = c.yg.empty() ? 0 : 1;
   a.x_atomic = c.xg_bcast ? 1 : 0;
   a.y_atomic = c.yg_bcast ? 1 : 0;
+  a.sph = c.sph;
+  a.sph_sb = c.sph_sb;
+  a.sph_sm = c.sph_sm;
+  a.sph_lmax = c.sph_lmax;
+  if (c.sph) {  // parts l = 0..lmax in order, one channel each, and no gradient with respect to them
+    if (n1max != 1 || (int)c.x.size() != c.sph_lmax + 1 || c.sph_lmax > kSphPointMaxL || !c.xg.empty()) return false;
+    for (size_t i = 0; i < c.x.size(); i++) if (c.x[i].l != (int)i) return false;
+  }
   return true;
 }
 

@@ -19,6 +19,9 @@ struct VecCall {
   bool xg_bcast = false, yg_bcast = false;
   bool dense_channels = true;  // every tensor has channel stride 2 floats
   bool vec_ok = true;          // 16-byte alignment of bases/strides/offsets of r (g) holds, offsets and n2 even
+  const float* sph = nullptr;  // fused first layer: x parts are the harmonics of these points (cell, 3), never read
+  long long sph_sb = 0, sph_sm = 0;
+  int sph_lmax = 0;
   bool in_vec_ok = true;       // 16-byte alignment of every x, y, xg, yg part (float4 access to the small operands)
 };
 

@@ -172,6 +172,17 @@ int gelib_SO3vec_addCGproduct_static(int nr, const gelib_tensor5* r, int nx, con
  * SO3part.spharm writes, python/src/gelib/SO3part.py:54-62). */
 int gelib_SO3vec_addSPharm(int nr, const gelib_tensor5* r, const gelib_tensor5* x, int flags, void* stream);
 
+/* Fused first layer: r (+)= CGproduct(u, y) with u the SO3vec whose part l, l = 0..lmax_x, is the spherical harmonics
+ * Y_l(X) in one channel -- the pipeline SO3part.spharm (python/src/gelib/SO3part.py:54-62, SO3/SO3part.hpp:150-156,
+ * 340-397) followed by SO3vec CGproduct (core/Gvec.hpp:311-321) -- without the harmonics ever being written to memory:
+ * the kernels generate them per point where they stage x.  X: real (batch, 1, 1, 3, 1).  y: parts with one channel count
+ * <= 32 and l <= 7 (GELIB_INVALID otherwise).  _back1 is the gradient with respect to y (points carry no gradient):
+ * yg += C g conj(u). */
+int gelib_SO3vec_addCGproduct_spharm(int nr, const gelib_tensor5* r, const gelib_tensor5* X, int lmax_x, int ny,
+                                     const gelib_tensor5* y, int flags, void* stream);
+int gelib_SO3vec_addCGproduct_spharm_back1(int ny, const gelib_tensor5* yg, int ng, const gelib_tensor5* g,
+                                           const gelib_tensor5* X, int lmax_x, int flags, void* stream);
+
 /* ---- callers of the path ------------------------------------------------------------------------ */
 
 /* Gather along one array dimension of an SO3partArr (message passing): for every outer index o and target t,
