@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libgelib_b200.so")
 
 GELIB_OK, GELIB_SKIPPED, GELIB_INVALID, GELIB_CUDA_ERROR = 0, 1, 2, 3
 GELIB_OVERWRITE = 1
+GELIB_FP64 = 2
 GELIB_MAX_PARTS = 16
 
 

@@ -12,11 +12,15 @@ import ctypes
 import torch
 
 from . import _lib
-from ._lib import GELIB_OVERWRITE, check, descriptor, descriptor_array, device_guard, lib, stream_of
+from ._lib import GELIB_FP64, GELIB_OVERWRITE, check, descriptor, descriptor_array, device_guard, lib, stream_of
 
 
 def _ints(v):
     return (ctypes.c_int * max(1, len(v)))(*v)
+
+
+def _flags(overwrite, fp64):
+    return (GELIB_OVERWRITE if overwrite else 0) | (GELIB_FP64 if fp64 else 0)
 
 
 def _one_device(*tensors):
@@ -210,23 +214,24 @@ class SO3part:
             return check(getattr(lib(), name)(ctypes.byref(da), ctypes.byref(db), ctypes.byref(dc), offs, flags,
                                               stream_of(a)))
 
-    def add_CGproduct(self, x, y, offs=0, *, overwrite=False):
-        return self._call3("gelib_SO3part_addCGproduct", self.t, x.t, y.t, offs, GELIB_OVERWRITE if overwrite else 0)
+    # fp64=True: coefficients and sums in double (GELIB_FP64), through the general strided kernels
+    def add_CGproduct(self, x, y, offs=0, *, overwrite=False, fp64=False):
+        return self._call3("gelib_SO3part_addCGproduct", self.t, x.t, y.t, offs, _flags(overwrite, fp64))
 
-    def add_CGproduct_back0(self, g, y, offs=0):
-        return self._call3("gelib_SO3part_addCGproduct_back0", self.t, g.t, y.t, offs)
+    def add_CGproduct_back0(self, g, y, offs=0, *, fp64=False):
+        return self._call3("gelib_SO3part_addCGproduct_back0", self.t, g.t, y.t, offs, _flags(False, fp64))
 
-    def add_CGproduct_back1(self, g, x, offs=0):
-        return self._call3("gelib_SO3part_addCGproduct_back1", self.t, g.t, x.t, offs)
+    def add_CGproduct_back1(self, g, x, offs=0, *, fp64=False):
+        return self._call3("gelib_SO3part_addCGproduct_back1", self.t, g.t, x.t, offs, _flags(False, fp64))
 
-    def add_DiagCGproduct(self, x, y, offs=0, *, overwrite=False):
-        return self._call3("gelib_SO3part_addDiagCGproduct", self.t, x.t, y.t, offs, GELIB_OVERWRITE if overwrite else 0)
+    def add_DiagCGproduct(self, x, y, offs=0, *, overwrite=False, fp64=False):
+        return self._call3("gelib_SO3part_addDiagCGproduct", self.t, x.t, y.t, offs, _flags(overwrite, fp64))
 
-    def add_DiagCGproduct_back0(self, g, y, offs=0):
-        return self._call3("gelib_SO3part_addDiagCGproduct_back0", self.t, g.t, y.t, offs)
+    def add_DiagCGproduct_back0(self, g, y, offs=0, *, fp64=False):
+        return self._call3("gelib_SO3part_addDiagCGproduct_back0", self.t, g.t, y.t, offs, _flags(False, fp64))
 
-    def add_DiagCGproduct_back1(self, g, x, offs=0):
-        return self._call3("gelib_SO3part_addDiagCGproduct_back1", self.t, g.t, x.t, offs)
+    def add_DiagCGproduct_back1(self, g, x, offs=0, *, fp64=False):
+        return self._call3("gelib_SO3part_addDiagCGproduct_back1", self.t, g.t, x.t, offs, _flags(False, fp64))
 
     @staticmethod
     def _back01(name, xg, yg, g, x, y, offs):
@@ -307,8 +312,8 @@ class SO3vec:
             return check(getattr(lib(), name)(len(ta), descriptor_array(ta), len(tb), descriptor_array(tb), len(tc),
                                               descriptor_array(tc), flags, stream_of(ta[0])))
 
-    def addCGproduct(self, x, y, *, overwrite=False):
-        return self._call3("gelib_SO3vec_addCGproduct", self, x, y, GELIB_OVERWRITE if overwrite else 0)
+    def addCGproduct(self, x, y, *, overwrite=False, fp64=False):
+        return self._call3("gelib_SO3vec_addCGproduct", self, x, y, _flags(overwrite, fp64))
 
     def addCGproduct_static(self, x, y, *, overwrite=False):
         """addCGproduct through the entry point that allocates no device memory (tables in a fixed 64 KB device
@@ -335,11 +340,11 @@ class SO3vec:
                                                                       descriptor_array(tg), ctypes.byref(dx), lmax_x, 0,
                                                                       stream_of(tg[0])))
 
-    def addCGproduct_back0(self, g, y):
-        return self._call3("gelib_SO3vec_addCGproduct_back0", self, g, y)
+    def addCGproduct_back0(self, g, y, *, fp64=False):
+        return self._call3("gelib_SO3vec_addCGproduct_back0", self, g, y, _flags(False, fp64))
 
-    def addCGproduct_back1(self, g, x):
-        return self._call3("gelib_SO3vec_addCGproduct_back1", self, g, x)
+    def addCGproduct_back1(self, g, x, *, fp64=False):
+        return self._call3("gelib_SO3vec_addCGproduct_back1", self, g, x, _flags(False, fp64))
 
     def addDiagCGproduct(self, x, y, *, overwrite=False):
         return self._call3("gelib_SO3vec_addDiagCGproduct", self, x, y, GELIB_OVERWRITE if overwrite else 0)

@@ -217,9 +217,10 @@ int run_product(const char* fn, bool diag, int mode, int nr, const gelib_tensor5
       return fail(GELIB_INVALID, fn, "the fused spherical-harmonics product takes y parts of one channel count <= 32 with l <= 7");
     return st;
   }
+  const bool fp64 = (flags & GELIB_FP64) != 0;  // double coefficients and sums: the general strided kernels
   if (mode == 0) {
     st = -1;
-    if (c.dense_channels && !c.r_bcast) {
+    if (c.dense_channels && !c.r_bcast && !fp64) {
       if (diag) {
         st = launch_diag_fwd(c, s);
       } else {
@@ -231,7 +232,7 @@ int run_product(const char* fn, bool diag, int mode, int nr, const gelib_tensor5
     return st;
   }
   st = -1;
-  if (c.dense_channels) {
+  if (c.dense_channels && !fp64) {
     if (diag) {
       st = launch_diag_bwd(c, s);
     } else {

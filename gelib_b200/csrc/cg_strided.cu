@@ -19,6 +19,7 @@ struct StridedArgs {
   CellGrid cg;
   const Triple* triples;
   const float* coeffs;
+  const double* coeffs64;  // the same table in double (GELIB_FP64), else nullptr
   int offs_extra;
   int diag;
   int atomic_out;  // forward only: output is broadcast, combine with atomics
@@ -27,8 +28,8 @@ struct StridedArgs {
 
 __device__ __forceinline__ float2 ld2(const float* p) { return *reinterpret_cast<const float2*>(p); }
 
-// mode 0: forward, 1: gradient wrt x, 2: gradient wrt y
-template <int MODE>
+// mode 0: forward, 1: gradient wrt x, 2: gradient wrt y.  ACC: float, or double for GELIB_FP64 (coefficients and sums).
+template <int MODE, typename ACC>
 __global__ void __launch_bounds__(256) cg_strided_kernel(const __grid_constant__ StridedArgs A) {
   const long long cell = blockIdx.x;
   const Triple t = A.triples[blockIdx.y];
@@ -37,7 +38,7 @@ __global__ void __launch_bounds__(256) cg_strided_kernel(const __grid_constant__
   const PartView& rp = A.r[t.ri];
   const int l1 = t.l1, l2 = t.l2, l = t.l;
   const int n1 = xp.n, n2 = yp.n;
-  const float* C = A.coeffs + t.coff;
+  const ACC* C = (sizeof(ACC) == 8 ? reinterpret_cast<const ACC*>(A.coeffs64) : reinterpret_cast<const ACC*>(A.coeffs)) + t.coff;
   float* xb = xp.base + cell_offset(xp, A.cg, cell);
   float* yb = yp.base + cell_offset(yp, A.cg, cell);
   float* rb = rp.base + cell_offset(rp, A.cg, cell) + (long long)(t.offs + A.offs_extra) * rp.sc;
@@ -54,23 +55,23 @@ __global__ void __launch_bounds__(256) cg_strided_kernel(const __grid_constant__
       // offset of this row's first coefficient in the band table
       int cpos = 0;
       for (int mm = -l; mm < m; mm++) cpos += max(0, min(l1, mm + l2) - max(-l1, mm - l2) + 1);
-      float sr = 0.f, si = 0.f;
+      ACC sr = 0, si = 0;
       for (int m1 = lo; m1 <= hi; m1++) {
-        const float c = C[cpos + (m1 - lo)];
+        const ACC c = C[cpos + (m1 - lo)];
         const float2 xv = ld2(xb + (long long)(m1 + l1) * xp.sm + (long long)a * xp.sc);
         const float2 yv = ld2(yb + (long long)(m - m1 + l2) * yp.sm + (long long)b * yp.sc);
-        const float cr = c * xv.x, ci = c * xv.y;
-        sr = fmaf(cr, yv.x, sr); sr = fmaf(-ci, yv.y, sr);
-        si = fmaf(cr, yv.y, si); si = fmaf(ci, yv.x, si);
+        const ACC cr = c * xv.x, ci = c * xv.y;
+        sr = fma(cr, (ACC)yv.x, sr); sr = fma(-ci, (ACC)yv.y, sr);
+        si = fma(cr, (ACC)yv.y, si); si = fma(ci, (ACC)yv.x, si);
       }
       float* p = rb + (long long)mi * rp.sm + (long long)ch * rp.sc;
       if (A.atomic_out) {
-        atomicAdd(p, sr);
-        atomicAdd(p + 1, si);
+        atomicAdd(p, (float)sr);
+        atomicAdd(p + 1, (float)si);
       } else if (A.overwrite) {
-        p[0] = sr; p[1] = si;
+        p[0] = (float)sr; p[1] = (float)si;
       } else {
-        p[0] += sr; p[1] += si;
+        p[0] = (float)(p[0] + sr); p[1] = (float)(p[1] + si);
       }
     }
   } else {
@@ -85,36 +86,36 @@ __global__ void __launch_bounds__(256) cg_strided_kernel(const __grid_constant__
     for (int e = threadIdx.x; e < total; e += blockDim.x) {
       const int mi = e / no, ch = e - mi * no;
       const int mo = mi - lo_l;
-      float sr = 0.f, si = 0.f;
+      ACC sr = 0, si = 0;
       for (int mt = -ot_l; mt <= ot_l; mt++) {
         const int m = mo + mt;
         if (m < -l || m > l) continue;
         const int m1 = MODE == 1 ? mo : mt;
         int cpos = 0;
         for (int mm = -l; mm < m; mm++) cpos += max(0, min(l1, mm + l2) - max(-l1, mm - l2) + 1);
-        const float c = C[cpos + (m1 - max(-l1, m - l2))];
+        const ACC c = C[cpos + (m1 - max(-l1, m - l2))];
         const float* grow = rb + (long long)(m + l) * rp.sm;
         const float* trow = tb + (long long)(mt + ot_l) * tp.sm;
         if (diag) {
           const float2 g = ld2(grow + (long long)ch * rp.sc);
           const float2 tv = ld2(trow + (long long)ch * tp.sc);
-          const float gr = c * g.x, gi = c * g.y;
-          sr = fmaf(gr, tv.x, sr); sr = fmaf(gi, tv.y, sr);
-          si = fmaf(gi, tv.x, si); si = fmaf(-gr, tv.y, si);
+          const ACC gr = c * g.x, gi = c * g.y;
+          sr = fma(gr, (ACC)tv.x, sr); sr = fma(gi, (ACC)tv.y, sr);
+          si = fma(gi, (ACC)tv.x, si); si = fma(-gr, (ACC)tv.y, si);
         } else {
           for (int k = 0; k < nt; k++) {
             const int gch = MODE == 1 ? ch * n2 + k : k * n2 + ch;
             const float2 g = ld2(grow + (long long)gch * rp.sc);
             const float2 tv = ld2(trow + (long long)k * tp.sc);
-            const float gr = c * g.x, gi = c * g.y;
-            sr = fmaf(gr, tv.x, sr); sr = fmaf(gi, tv.y, sr);
-            si = fmaf(gi, tv.x, si); si = fmaf(-gr, tv.y, si);
+            const ACC gr = c * g.x, gi = c * g.y;
+            sr = fma(gr, (ACC)tv.x, sr); sr = fma(gi, (ACC)tv.y, sr);
+            si = fma(gi, (ACC)tv.x, si); si = fma(-gr, (ACC)tv.y, si);
           }
         }
       }
       float* p = ob + (long long)mi * op.sm + (long long)ch * op.sc;
-      atomicAdd(p, sr);
-      atomicAdd(p + 1, si);
+      atomicAdd(p, (float)sr);
+      atomicAdd(p + 1, (float)si);
     }
   }
 }
@@ -125,13 +126,25 @@ int launch_cg_strided(const VecCall& c, int mode, cudaStream_t s) {
   static const char* fn = "SO3vec_addCGproduct(strided)";
   const std::vector<PartView>& xv = mode == 1 ? c.xg : c.x;
   const std::vector<PartView>& yv = mode == 2 ? c.yg : c.y;
-  std::vector<int> key = {2 /*family*/, c.diag ? 1 : 0, (int)xv.size(), (int)yv.size(), (int)c.r.size()};
+  const bool fp64 = (c.flags & GELIB_FP64) != 0;
+  std::vector<int> key = {2 /*family*/, (c.diag ? 1 : 0) | (fp64 ? 2 : 0), (int)xv.size(), (int)yv.size(), (int)c.r.size()};
   for (const auto& p : xv) { key.push_back(p.l); key.push_back(p.n); }
   for (const auto& p : yv) { key.push_back(p.l); key.push_back(p.n); }
   for (const auto& p : c.r) key.push_back(p.l);
   const auto xs = sig_of(xv), ys = sig_of(yv), rs = sig_of(c.r);
   const bool diag = c.diag;
-  DevicePlan* plan = get_plan(key, [&](DevicePlan& p) { build_schedule(xs, ys, rs, diag, true, &p.sched); });
+  DevicePlan* plan = get_plan(key, [&](DevicePlan& p) {
+    build_schedule(xs, ys, rs, diag, true, &p.sched);
+    if (fp64) {  // the same band tables in double, stored behind the plan's float table slot
+      std::vector<double> c64;
+      for (const Triple& t : p.sched.triples)
+        for (int m = -t.l; m <= t.l; m++)
+          for (int m1 = std::max<int>(-t.l1, m - t.l2); m1 <= std::min<int>(t.l1, m + t.l2); m1++)
+            c64.push_back(cg_coefficient(t.l1, t.l2, t.l, m1, m - m1));
+      p.h_floats.resize(2 * c64.size());
+      memcpy(p.h_floats.data(), c64.data(), c64.size() * sizeof(double));
+    }
+  });
   if (!plan) return GELIB_CUDA_ERROR;
   if (plan->ntriples == 0 || c.cg.ncells == 0) return GELIB_OK;
   if (plan->ntriples > 65535) return fail(GELIB_SKIPPED, fn, "more than 65535 triples");
@@ -144,14 +157,21 @@ int launch_cg_strided(const VecCall& c, int mode, cudaStream_t s) {
   a.cg = c.cg;
   a.triples = plan->triples;
   a.coeffs = plan->coeffs;
+  a.coeffs64 = fp64 ? reinterpret_cast<const double*>(plan->floats) : nullptr;
   a.offs_extra = c.offs_extra;
   a.diag = c.diag ? 1 : 0;
   a.atomic_out = c.r_bcast ? 1 : 0;
   a.overwrite = (c.flags & GELIB_OVERWRITE) && !c.r_bcast ? 1 : 0;
   const dim3 grid((unsigned)c.cg.ncells, (unsigned)plan->ntriples);
-  if (mode == 0) cg_strided_kernel<0><<<grid, 256, 0, s>>>(a);
-  else if (mode == 1) cg_strided_kernel<1><<<grid, 256, 0, s>>>(a);
-  else cg_strided_kernel<2><<<grid, 256, 0, s>>>(a);
+  if (fp64) {
+    if (mode == 0) cg_strided_kernel<0, double><<<grid, 256, 0, s>>>(a);
+    else if (mode == 1) cg_strided_kernel<1, double><<<grid, 256, 0, s>>>(a);
+    else cg_strided_kernel<2, double><<<grid, 256, 0, s>>>(a);
+  } else {
+    if (mode == 0) cg_strided_kernel<0, float><<<grid, 256, 0, s>>>(a);
+    else if (mode == 1) cg_strided_kernel<1, float><<<grid, 256, 0, s>>>(a);
+    else cg_strided_kernel<2, float><<<grid, 256, 0, s>>>(a);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return check_cuda(e, fn, "strided kernel launch");
   count_launch();
@@ -225,11 +245,12 @@ int launch_cg_strided_static(const VecCall& c, cudaStream_t s) {
   a.cg = c.cg;
   a.triples = reinterpret_cast<const Triple*>(dev);
   a.coeffs = reinterpret_cast<const float*>(dev + tbytes);
+  a.coeffs64 = nullptr;
   a.offs_extra = c.offs_extra;
   a.diag = c.diag ? 1 : 0;
   a.atomic_out = c.r_bcast ? 1 : 0;
   a.overwrite = (c.flags & GELIB_OVERWRITE) && !c.r_bcast ? 1 : 0;
-  cg_strided_kernel<0><<<dim3((unsigned)c.cg.ncells, (unsigned)ntr), 256, 0, s>>>(a);
+  cg_strided_kernel<0, float><<<dim3((unsigned)c.cg.ncells, (unsigned)ntr), 256, 0, s>>>(a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return check_cuda(e, fn, "strided kernel launch");
   count_launch();

@@ -40,8 +40,12 @@ enum { GELIB_OK = 0, GELIB_SKIPPED = 1, GELIB_INVALID = 2, GELIB_CUDA_ERROR = 3 
 
 /* flags */
 enum {
-  GELIB_OVERWRITE = 1 /* forward only: the output block is written, not accumulated into, which
-                         saves the read-modify-write and the caller's zero fill */
+  GELIB_OVERWRITE = 1, /* forward only: the output block is written, not accumulated into, which
+                          saves the read-modify-write and the caller's zero fill */
+  GELIB_FP64 = 2       /* products and gradients: Clebsch-Gordan coefficients kept in double and every sum accumulated in
+                          double, rounded to float once on output.  The reference's bank is single precision only
+                          (SO3/SO3CGbank.hpp:52); this is the accuracy path for long accumulations (large l, many
+                          channels).  It runs the general strided kernels, at a fraction of the tiled kernels' speed. */
 };
 
 #define GELIB_MAX_PARTS 16 /* most parts (distinct l) one SO3vec argument may have */

@@ -161,3 +161,41 @@ def test_fused_spharm_cg_first_layer(G, oracle):
     wide = G.SO3vec(G.SO3part(crandn(1, B, 3, 64).cuda()))
     with pytest.raises(RuntimeError, match="fused spherical-harmonics"):
         G.SO3vec.spharm_CGproduct(2, Xd, wide, 2)
+
+
+def test_fp64_option_keeps_double_coefficients_and_sums(G):
+    """GELIB_FP64: against a complex128 evaluation with double coefficients the result is exact to float rounding of the
+    output, for the forward product and both gradients at l = 8 with 48 channels (sums of up to 17 x 48 terms)."""
+    import ctypes
+    B, l1, l2, l, n = 2, 8, 8, 8, 48
+    x, y, g = crandn(1, B, 2 * l1 + 1, n), crandn(2, B, 2 * l2 + 1, n), crandn(3, B, 2 * l + 1, n * n)
+    L = G._lib.lib()
+    C = np.zeros((2 * l1 + 1, 2 * l2 + 1))
+    for m1 in range(-l1, l1 + 1):
+        for m2 in range(-l2, l2 + 1):
+            if abs(m1 + m2) <= l:
+                C[m1 + l1, m2 + l2] = L.gelib_CGcoefficient(l1, l2, l, m1, m2)
+    C3 = np.zeros((2 * l1 + 1, 2 * l2 + 1, 2 * l + 1))
+    for m1 in range(-l1, l1 + 1):
+        for m2 in range(-l2, l2 + 1):
+            if abs(m1 + m2) <= l:
+                C3[m1 + l1, m2 + l2, m1 + m2 + l] = C[m1 + l1, m2 + l2]
+    xn, yn, gn = np_c(x).astype(np.complex128), np_c(y).astype(np.complex128), np_c(g).astype(np.complex128)
+    want = np.einsum("abm,zai,zbj->zmij", C3, xn, yn).reshape(B, 2 * l + 1, n * n)
+    g4 = gn.reshape(B, 2 * l + 1, n, n)
+    xg_w = np.einsum("abm,zmij,zbj->zai", C3, g4, yn.conj())
+    yg_w = np.einsum("abm,zmij,zai->zbj", C3, g4, xn.conj())
+    view = G.backend.SO3part.view
+    xd, yd, gd = x.cuda(), y.cuda(), g.cuda()
+
+    def run(fp64):
+        r = torch.zeros(B, 2 * l + 1, n * n, dtype=torch.complex64, device="cuda")
+        view(r).add_CGproduct(view(xd), view(yd), fp64=fp64)
+        xg, yg = torch.zeros_like(xd), torch.zeros_like(yd)
+        view(xg).add_CGproduct_back0(view(gd), view(yd), fp64=fp64)
+        view(yg).add_CGproduct_back1(view(gd), view(xd), fp64=fp64)
+        return [float(np.abs(a.cpu().numpy() - w).max() / np.abs(w).max()) for a, w in ((r, want), (xg, xg_w), (yg, yg_w))]
+
+    e64, e32 = run(True), run(False)
+    assert max(e64) < 1.5e-7, e64            # float rounding of the stored result only
+    assert max(e32) < 1e-5 and e64[1] < e32[1] and e64[2] < e32[2], (e64, e32)
