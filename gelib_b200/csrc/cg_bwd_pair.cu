@@ -46,7 +46,9 @@ namespace {
 
 using namespace tc;
 
-constexpr int kConsumers = 8;                        // 2 roles x 4 quarter tiles
+constexpr int kSplit = 4;                            // warps per role: each takes 32 / kSplit of the other channel index (8 was tried: 19.7 ms)
+constexpr int kCW = 32 / kSplit;                     // complex numbers per lane and slab
+constexpr int kConsumers = 2 * kSplit;
 constexpr int kProducers = 4;                        // copy warps, one per scheduler; each moves a quarter of every slab
 constexpr int kThreads = (kConsumers + kProducers) * 32;
 constexpr int kRowPitch = 272;                       // bytes per staged slab row: 32 complex + 16
@@ -93,13 +95,16 @@ __device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
 
 // H = sum_l c_l G_l for the warp's 8 complex numbers, contracted with the conjugate of the other operand's 8.
 template <int LM>
-__device__ __forceinline__ void contract(const float (&G)[kGroupSlabs][16], const float4 c, const float4 (&w)[4], float& sr,
+__device__ __forceinline__ void contract(const float (&G)[kGroupSlabs][2 * kCW], const float4 c, const float4 (&w)[kCW / 2], float& sr,
                                          float& si) {
-  const float v[16] = {w[0].x, w[0].y, w[0].z, w[0].w, w[1].x, w[1].y, w[1].z, w[1].w,
-                       w[2].x, w[2].y, w[2].z, w[2].w, w[3].x, w[3].y, w[3].z, w[3].w};
-  float H[16];
+  float v[2 * kCW];
 #pragma unroll
-  for (int e = 0; e < 16; e++) {
+  for (int t = 0; t < kCW / 2; t++) {
+    v[4 * t] = w[t].x; v[4 * t + 1] = w[t].y; v[4 * t + 2] = w[t].z; v[4 * t + 3] = w[t].w;
+  }
+  float H[2 * kCW];
+#pragma unroll
+  for (int e = 0; e < 2 * kCW; e++) {
     if (LM == 1) {
       H[e] = G[0][e];
     } else {
@@ -112,7 +117,7 @@ __device__ __forceinline__ void contract(const float (&G)[kGroupSlabs][16], cons
   }
   float sr0 = 0.f, si0 = 0.f, sr1 = 0.f, si1 = 0.f;
 #pragma unroll
-  for (int e = 0; e < 16; e += 4) {
+  for (int e = 0; e < 2 * kCW; e += 4) {
     sr0 = fmaf(H[e], v[e], sr0);
     si0 = fmaf(H[e + 1], v[e], si0);
     sr1 = fmaf(H[e + 2], v[e + 2], sr1);
@@ -136,15 +141,15 @@ __device__ __forceinline__ void contract(const float (&G)[kGroupSlabs][16], cons
 // for the first entry (4 x 16 bytes), ostep its signed step; a: the lane's slot in the warp's private accumulator
 // row of the first entry, astep its signed step.
 struct BandEntry {
-  float4 c, w[4];
+  float4 c, w[kCW / 2];
 };
 __device__ __forceinline__ void load_entry(BandEntry& e, const unsigned char* smem, int coef, int o) {
   e.c = *reinterpret_cast<const float4*>(smem + coef);
 #pragma unroll
-  for (int t = 0; t < 4; t++) e.w[t] = *reinterpret_cast<const float4*>(smem + o + 16 * t);
+  for (int t = 0; t < kCW / 2; t++) e.w[t] = *reinterpret_cast<const float4*>(smem + o + 16 * t);
 }
 template <int LM>
-__device__ __forceinline__ void use_entry(const float (&G)[kGroupSlabs][16], const BandEntry& e, unsigned char* smem, int a) {
+__device__ __forceinline__ void use_entry(const float (&G)[kGroupSlabs][2 * kCW], const BandEntry& e, unsigned char* smem, int a) {
   float2 s = *reinterpret_cast<float2*>(smem + a);
   float r, i;
   contract<LM>(G, e.c, e.w, r, i);
@@ -153,7 +158,7 @@ __device__ __forceinline__ void use_entry(const float (&G)[kGroupSlabs][16], con
   *reinterpret_cast<float2*>(smem + a) = s;
 }
 template <int LM>
-__device__ __forceinline__ void band_loop(const float (&G)[kGroupSlabs][16], unsigned char* smem, int coef, int cnt, int o,
+__device__ __forceinline__ void band_loop(const float (&G)[kGroupSlabs][2 * kCW], unsigned char* smem, int coef, int cnt, int o,
                                           int ostep, int a, int astep) {
   BandEntry A, B;
   load_entry(A, smem, coef, o);
@@ -311,13 +316,13 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
     if (!ok && lane == 0) *A.status = 1;
   } else {
     // ---- consumers
-    const int role = warp >> 2, q = warp & 3;
+    const int role = warp / kSplit, q = warp % kSplit;
     const bool active = role == 0 ? (A.do_x != 0) : (A.do_y != 0);
     float2* mine = priv + (warp * J) * 32 + lane;
     const int mine_off = kHeaderBytes + 8 * A.cell_floats + (warp * J * 32 + lane) * 8;  // the same as a byte offset
     // where the warp's quarter of a slab sits inside a slot: xg warps read row `lane`, columns 8q..8q+7 (16-byte
     // loads, lanes 272 bytes apart); yg warps read rows 8q..8q+7, column `lane` (8-byte loads, lanes adjacent)
-    const int goffs = role == 0 ? lane * kRowPitch + q * 64 : 8 * q * kRowPitch + lane * 8;
+    const int goffs = role == 0 ? lane * kRowPitch + q * (8 * kCW) : kCW * q * kRowPitch + lane * 8;
     bool ok = true;
     int st = 0, phase = 0;
     for (int gi = 0; gi < A.ngroups; gi++) {
@@ -328,14 +333,14 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
         const int4 d0 = *reinterpret_cast<const int4*>(sbase + kDescOff + role * 32);
         const int4 d1 = *reinterpret_cast<const int4*>(sbase + kDescOff + role * 32 + 16);
         const int nslab = d0.x & 7, cnt = (d0.x >> 8) & 0xff;
-        float G[kGroupSlabs][16];
+        float G[kGroupSlabs][2 * kCW];
         if (role == 0) {
 #pragma unroll
           for (int s = 0; s < kGroupSlabs; s++) {
             if (s < nslab) {
               const float4* gp = reinterpret_cast<const float4*>(sbase + s * kSlotBytes + goffs);
 #pragma unroll
-              for (int t = 0; t < 4; t++) {
+              for (int t = 0; t < kCW / 2; t++) {
                 const float4 w = gp[t];
                 G[s][4 * t] = w.x; G[s][4 * t + 1] = w.y; G[s][4 * t + 2] = w.z; G[s][4 * t + 3] = w.w;
               }
@@ -347,7 +352,7 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
             if (s < nslab) {
               const unsigned char* gp = sbase + s * kSlotBytes + goffs;
 #pragma unroll
-              for (int r = 0; r < 8; r++) {
+              for (int r = 0; r < kCW; r++) {
                 const float2 w = *reinterpret_cast<const float2*>(gp + r * kRowPitch);
                 G[s][2 * r] = w.x; G[s][2 * r + 1] = w.y;
               }
@@ -355,7 +360,7 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
           }
         }
         const int sb = ring_off + st * kStageBytes;
-        const int o = d0.y + q * 64, a = mine_off + d0.w;
+        const int o = d0.y + q * (8 * kCW), a = mine_off + d0.w;
         switch (nslab) {
           case 1: band_loop<1>(G, smem_raw, sb + kCoefOff, cnt, o, d0.z, a, d1.x); break;
           case 2: band_loop<2>(G, smem_raw, sb + kCoefOff, cnt, o, d0.z, a, d1.x); break;
