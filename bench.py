@@ -93,7 +93,8 @@ def kernel_name(args, dom):
         return "cg_fwd_tc_kernel" if tc else "cg_fwd_kernel"
     if args.bwd_kernel == "tcgen05":
         return "cg_bwd_tc_kernel"
-    pair = args.bwd_kernel in ("auto", "pair") and args.workload in ("cfg1", "cfg2", "cfg3")
+    pair = (args.bwd_kernel == "pair" and args.workload in ("cfg1", "cfg2", "cfg3")) or (
+        args.bwd_kernel == "auto" and args.workload in ("cfg2", "cfg3"))   # cfg1 has 5 groups per cell: below the threshold
     return "cg_bwd_pair_kernel" if pair else "cg_bwd_kernel"
 
 

@@ -356,7 +356,7 @@ int launch_cg_bwd(const VecCall& c, cudaStream_t s) {
     if (rc != -1) return rc;
     if (mode == kBwdTcStrict) return fail(GELIB_INVALID, fn, "the call does not qualify for the tcgen05 kernel");
   } else if (mode != kBwdSimt) {
-    const int rc = launch_cg_bwd_pair(c, s);
+    const int rc = launch_cg_bwd_pair(c, s, mode == kBwdAuto ? 32 : 0);
     if (rc != -1) return rc;
     if (mode == kBwdPairStrict) return fail(GELIB_INVALID, fn, "the call does not qualify for the pair kernel");
   }

@@ -396,7 +396,7 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
 }  // namespace
 
 // Returns -1 when the call does not qualify (the caller then takes the kernel of cg_bwd.cu).
-int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s) {
+int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s, int min_groups) {
   static const char* fn = "SO3vec_addCGproduct_back";
   if (!c.vec_ok) return -1;
   if (c.x.empty() || c.y.empty() || c.r.empty()) return -1;
@@ -507,6 +507,8 @@ int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s) {
   });
   if (!plan) return GELIB_CUDA_ERROR;
   if (plan->nitems == 0 || c.cg.ncells == 0) return GELIB_OK;
+  // a cell with only a few groups does not fill the pipeline of 12 warps: the one-slab-per-warp kernel is faster there
+  if (min_groups > 0 && plan->nitems / kRec < min_groups) return -1;
 
   a.cg = c.cg;
   a.recs = plan->items;

@@ -36,7 +36,7 @@ int launch_cg_fwd(const VecCall& c, cudaStream_t s);
 int launch_cg_fwd_tc(const VecCall& c, cudaStream_t s, int min_slabs);  // tcgen05 kernel; -1 when the call does not qualify or has fewer slabs per cell
 int launch_cg_bwd(const VecCall& c, cudaStream_t s);
 int launch_cg_bwd_tc(const VecCall& c, cudaStream_t s);  // tcgen05 kernel; -1 when the call does not qualify
-int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s);  // uncoupled-gradient kernel; -1 when the call does not qualify
+int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s, int min_groups);  // uncoupled-gradient kernel; -1 when the call does not qualify or has fewer groups per cell
 int launch_cg_narrow_bwd(const VecCall& c, cudaStream_t s);
 int launch_cg_narrow_fwd(const VecCall& c, cudaStream_t s);  // x with at most 4 channels; -1 when the call does not qualify
 int launch_cg_strided(const VecCall& c, int mode, cudaStream_t s);  // mode 0 fwd, 1 back0, 2 back1

@@ -553,6 +553,61 @@ def test_part_beyond_2_to_31_floats(G, oracle, opt):
     torch.cuda.empty_cache()
 
 
+def test_views_that_are_only_8_byte_aligned(G, oracle):
+    """x, y taken as channel slices [1:33] of wider tensors (base 8 bytes off a 16-byte boundary, row pitch 66 floats)
+    under the default kernel choice: the kernels with 16-byte accesses must not be chosen for them, and the result is
+    the oracle's, forward and backward."""
+    B, tau, maxl = 3, {l: 32 for l in range(3)}, 2
+    xw = {l: crandn(30 + l, B, 2 * l + 1, 34) for l in tau}
+    yw = {l: crandn(40 + l, B, 2 * l + 1, 33) for l in tau}
+    xd = [t.cuda()[:, :, 1:33] for t in xw.values()]
+    yd = [t.cuda()[:, :, 1:33] for t in yw.values()]
+    assert xd[0].data_ptr() % 16 == 8
+    xn = {l: np_c(t[:, :, 1:33]) for l, t in xw.items()}
+    yn = {l: np_c(t[:, :, 1:33]) for l, t in yw.items()}
+    tau_r = oracle.cg_type(tau, tau, maxl, False)
+    want = {l: np.zeros((B, 2 * l + 1, n), np.complex64) for l, n in tau_r.items()}
+    oracle.vec_cg(want, xn, yn, False)
+    gb = G.backend
+    xv, yv = gb.SO3vec.view(xd), gb.SO3vec.view(yd)
+    rs = [torch.empty(B, 2 * l + 1, n, dtype=torch.complex64, device="cuda") for l, n in tau_r.items()]
+    gb.SO3vec.view(rs).addCGproduct(xv, yv, overwrite=True)
+    for p, (l, w) in zip(rs, want.items()):
+        assert rel_err(p, w) < TOL, l
+    g = {l: crandn(50 + l, B, 2 * l + 1, n) for l, n in tau_r.items()}
+    xg_w, yg_w = {l: np.zeros_like(t) for l, t in xn.items()}, {l: np.zeros_like(t) for l, t in yn.items()}
+    oracle.vec_cg_back0(xg_w, {l: np_c(t) for l, t in g.items()}, yn, False)
+    oracle.vec_cg_back1(yg_w, {l: np_c(t) for l, t in g.items()}, xn, False)
+    xgw = [torch.zeros(B, 2 * l + 1, 34, dtype=torch.complex64, device="cuda") for l in tau]
+    ygw = [torch.zeros(B, 2 * l + 1, 33, dtype=torch.complex64, device="cuda") for l in tau]
+    gb.SO3vec.addCGproduct_back01(gb.SO3vec.view([t[:, :, 1:33] for t in xgw]), gb.SO3vec.view([t[:, :, 1:33] for t in ygw]),
+                                  gb.SO3vec.view([t.cuda() for t in g.values()]), xv, yv)
+    for t, w in zip(xgw, xg_w.values()):
+        assert rel_err(t[:, :, 1:33], w) < TOL_BIG and float(t[:, :, 0].abs().max()) == 0.0 and float(t[:, :, 33].abs().max()) == 0.0
+    for t, w in zip(ygw, yg_w.values()):
+        assert rel_err(t[:, :, 1:33], w) < TOL_BIG and float(t[:, :, 0].abs().max()) == 0.0
+
+
+def test_skipped_product_returns_zeros_like_the_reference(G, capfd):
+    """A product the reference GELIB_SKIPs (l outside |l1-l2|..l1+l2) leaves its zero-initialised output untouched
+    (python/src/gelib/SO3part.py:183-185); the autograd layer allocates uninitialised memory, so it must zero it."""
+    torch.manual_seed(2)
+    x, y = G.SO3part.randn(3, 1, 4, device="cuda"), G.SO3part.randn(3, 1, 4, device="cuda")
+    for _ in range(3):   # whatever the allocator hands back
+        junk = torch.full((3, 7, 16), 5.0 + 1.0j, dtype=torch.complex64, device="cuda")
+        del junk
+        z = G.CGproduct(x, y, 3)
+        assert list(z.shape) == [3, 7, 16] and float(z.abs().max()) == 0.0
+    assert "skipped" in capfd.readouterr().err
+    # an output broadcast over cells cannot be overwritten: refused, not silently accumulated into garbage
+    r = torch.zeros(1, 5, 16, dtype=torch.complex64, device="cuda")
+    with pytest.raises(RuntimeError, match="GELIB_OVERWRITE"):
+        view(G, r).add_CGproduct(view(G, x), view(G, y), overwrite=True)
+    # x with a size-1 array dimension against y with 3: the output takes the larger
+    xa, ya = G.SO3partArr.randn(2, [1], 1, 2, device="cuda"), G.SO3partArr.randn(2, [3], 1, 2, device="cuda")
+    assert list(G.CGproduct(xa, ya, 1).shape) == [2, 3, 3, 4]
+
+
 # ---- spherical harmonics --------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("L", [0, 1, 2, 4, 6, 8, 11, 14])

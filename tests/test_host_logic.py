@@ -156,3 +156,52 @@ def test_python_surface_matches_reference_names():
     assert torch.allclose(R @ R.t(), torch.eye(3), atol=1e-5) and abs(float(torch.det(R)) - 1) < 1e-5
     D = G.SO3irrep(3).matrix(R)
     assert torch.allclose(D @ D.conj().t(), torch.eye(7, dtype=torch.complex64), atol=1e-5)
+
+
+def test_gather_map_csr_and_transpose():
+    """gather_map keeps targets -> sources as CSR and the transpose for the gradient; three constructors agree."""
+    import torch
+    from gelib_b200.backend import gather_map
+    m = gather_map.sources_targets([0, 1, 1, 4, 2], [3, 0, 3, 3, 1], n_in=5, n_out=4)
+    ptr, col = m._fwd
+    assert ptr.tolist() == [0, 1, 2, 2, 5] and col.tolist() == [1, 2, 0, 1, 4]
+    bptr, bcol = m._bwd
+    assert bptr.tolist() == [0, 1, 3, 4, 4, 5] and bcol.tolist() == [3, 0, 3, 1, 3]
+    M = torch.zeros(4, 5)
+    for s, t in zip([0, 1, 1, 4, 2], [3, 0, 3, 3, 1]):
+        M[t, s] = 1
+    m2 = gather_map.from_matrix(M, 5, 4)
+    assert m2._fwd[0].tolist() == ptr.tolist() and m2._fwd[1].tolist() == col.tolist()
+    assert m.d_in() == 5 and m.d_out() == 4
+    r = gather_map.random(6, 3, 0.5, generator=torch.Generator().manual_seed(1))
+    assert r.d_in() == 6 and r.d_out() == 3 and int(r._fwd[0][-1]) == int(r._bwd[0][-1])
+
+
+def test_o3_type_calculus_and_call_plan():
+    """O(3) bookkeeping on the host: index order 2l + [p = -1] (O3/O3index.hpp:51-53), p = p1 p2
+    (O3/O3group.hpp:38-44), and the slices of the per-(x part, y parity sector) calls tile every output part exactly."""
+    from gelib_b200.O3 import O3type, _sector_calls
+    tx = O3type({(1, -1): 3, (0, 1): 2, (1, 1): 1})
+    assert list(tx.parts) == [(0, 1), (1, 1), (1, -1)]
+    ty = O3type({(0, -1): 2, (1, 1): 2, (2, -1): 1})
+    tr = tx.CGproduct(ty, 2)
+    want = {}
+    for (l1, p1), n1 in tx.parts.items():
+        for (l2, p2), n2 in ty.parts.items():
+            for l in range(abs(l1 - l2), min(l1 + l2, 2) + 1):
+                want[(l, p1 * p2)] = want.get((l, p1 * p2), 0) + n1 * n2
+    assert tr.parts == dict(sorted(want.items(), key=lambda kv: 2 * kv[0][0] + (kv[0][1] == -1)))
+    xmus, ymus = list(tx.parts), list(ty.parts)
+    calls = _sector_calls(xmus, list(tx.parts.values()), ymus, list(ty.parts.values()), tr.parts, 2, False)
+    covered = {mu: [] for mu in tr.parts}
+    for i, js, p, slices in calls:
+        assert all(ymus[j][1] * xmus[i][1] == p for j in js)
+        for l, (o, w) in slices.items():
+            covered[(l, p)].append((o, w))
+    for mu, segs in covered.items():
+        segs.sort()
+        pos = 0
+        for o, w in segs:
+            assert o == pos
+            pos += w
+        assert pos == tr.parts[mu]
