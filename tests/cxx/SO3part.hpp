@@ -1,4 +1,4 @@
-// Stand-in for the two GElib / cnine types that the binding of INTEGRATION.md touches, so that its translation unit
+// Stand-in for the two GElib / cnine types that the binding include/SO3part_b200.cpp touches, so that its translation unit
 // can be compiled and run without the cnine sources (an un-vendored submodule of GElib).  Only what that binding uses:
 // arr, dims, strides (in elements), get_arr(), canonicalize_to_5d() (core/Gpart.hpp:450-469: (b, 2l+1, n) becomes
 // (b, 1, 1, 2l+1, n) with zero strides on the inserted grid dimensions) and cnine::CoutLock.

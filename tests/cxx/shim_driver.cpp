@@ -1,4 +1,4 @@
-// Calls the four reference-signature functions of the binding shown in INTEGRATION.md (SO3/SO3part.hpp:33-39 of
+// Calls the four reference-signature functions of the binding include/SO3part_b200.cpp (SO3/SO3part.hpp:33-39 of
 // GElib) on dense device buffers, so that a test can drive them from Python through ctypes.
 #include "SO3part.hpp"
 

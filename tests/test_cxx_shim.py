@@ -1,12 +1,11 @@
-"""The C++ binding a GElib maintainer adds (the `cuda/SO3part_b200.cpp` listing of INTEGRATION.md), compiled verbatim.
+"""The C++ binding a GElib maintainer adds (include/SO3part_b200.cpp, which replaces four files of GElib's cuda/).
 
-The listing is cut out of INTEGRATION.md, compiled with g++ against include/gelib_b200.h and a stand-in for the two
-cnine / GElib types it touches (tests/cxx/SO3part.hpp), linked with the library, and driven through the four
-reference signatures (SO3/SO3part.hpp:33-39 of GElib): forward, back0, back1, spherical harmonics.
+The file is compiled as it is with g++ against include/gelib_b200.h and a stand-in for the two cnine / GElib types it
+touches (tests/cxx/SO3part.hpp), linked with the library, and driven through the four reference signatures
+(SO3/SO3part.hpp:33-39 of GElib): forward, back0, back1, spherical harmonics.
 """
 import ctypes
 import os
-import re
 import subprocess
 
 import numpy as np
@@ -26,12 +25,7 @@ def build_shim():
     if not os.path.exists(_lib.LIB_PATH):
         build.build()
     os.makedirs(OUT, exist_ok=True)
-    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
-    m = re.search(r"```cpp\n(// cuda/SO3part_b200\.cpp.*?)```", text, re.S)
-    assert m, "the binding listing is missing from INTEGRATION.md"
-    src = os.path.join(OUT, "SO3part_b200.cpp")
-    with open(src, "w") as f:
-        f.write(m.group(1))
+    src = os.path.join(ROOT, "include", "SO3part_b200.cpp")
     so = os.path.join(OUT, "libgelib_shim.so")
     libdir = os.path.dirname(_lib.LIB_PATH)
     cmd = ["g++", "-std=c++17", "-O1", "-shared", "-fPIC", "-I", CXX, "-I", os.path.join(ROOT, "include"),
