@@ -407,3 +407,112 @@ def SO3CGmatrix(l1, l2, l):
 
 def kernel_launch_count():
     return int(lib().gelib_kernel_launch_count())
+
+
+# ---- the remaining names GElib's Python package takes from gelib_base ----------------------------------------------
+# (python/src/gelib/SO3element.py:31, SO3irrep.py:22-34, O3element.py, O3irrep.py, O3part.py:118, O3vec.py:101-102)
+
+
+class _Element:
+    """What ``gelib_base.SO3element`` / ``O3element`` hand to Python: a 3x3 matrix with ``.torch()``."""
+
+    def __init__(self, t):
+        self.t = t
+
+    def torch(self):
+        return self.t
+
+    @classmethod
+    def view(cls, t):
+        return cls(t)
+
+
+class SO3element(_Element):
+
+    @classmethod
+    def random(cls):
+        from .SO3element import SO3element as E
+        return cls(E.random().as_subclass(torch.Tensor))
+
+
+class O3element(_Element):
+
+    @classmethod
+    def random(cls):
+        from .O3 import O3element as E
+        return cls(E.random().as_subclass(torch.Tensor))
+
+
+class SO3irrep:
+    """``gelib_base.SO3irrep``: matrix(element view) or matrix(alpha, beta, gamma) -> (2l+1, 2l+1) complex64."""
+
+    def __init__(self, l):
+        self.l = l
+
+    def matrix(self, *args):
+        from .SO3irrep import euler_zyz
+        if len(args) == 3:
+            a, b, c = args
+        else:
+            R = args[0].t if isinstance(args[0], _Element) else args[0]
+            a, b, c = euler_zyz(R.detach().cpu().numpy())
+        return SO3irrep_matrix(self.l, a, b, c)
+
+    def __repr__(self):
+        return "<GElib::SO3irrep(l=%d)>" % self.l
+
+
+class O3irrep:
+
+    def __init__(self, l, p):
+        self.l, self.p = l, p
+
+    def matrix(self, *args):
+        from .O3 import O3irrep as I
+        if len(args) >= 3:
+            return I(self.l, self.p).matrix(list(args[:3]), p=args[3] if len(args) > 3 else 1)
+        R = args[0].t if isinstance(args[0], _Element) else args[0]
+        return I(self.l, self.p).matrix(R)
+
+    def __repr__(self):
+        return "<GElib::O3irrep(l=%d,p=%d)>" % (self.l, self.p)
+
+
+class O3type:
+
+    def __init__(self, x=None):
+        from .O3 import O3type as T
+        self.obj = T(x)
+
+    def get_parts(self):
+        return self.obj.get_parts()
+
+    def CGproduct(self, y, maxl=-1):
+        r = O3type()
+        r.obj = self.obj.CGproduct(y.obj, maxl)
+        return r
+
+    def DiagCGproduct(self, y, maxl=-1):
+        r = O3type()
+        r.obj = self.obj.DiagCGproduct(y.obj, maxl)
+        return r
+
+    def __repr__(self):
+        return repr(self.obj)
+
+    __str__ = __repr__
+
+
+class O3part(SO3part):
+    """``gelib_base.O3part.view(t, mu)``: the SO(3) view plus the parity (O3/O3part.hpp:222-269 forwards every product)."""
+
+    def __init__(self, t, mu=None):
+        super().__init__(t)
+        self.mu = mu
+
+    @staticmethod
+    def view(t, mu=None):
+        return O3part(t, mu)
+
+    def __repr__(self):
+        return "<GElib::O3part(l=%d,n=%d)>" % (self.getl(), self.getn())

@@ -205,3 +205,43 @@ def test_o3_type_calculus_and_call_plan():
             assert o == pos
             pos += w
         assert pos == tr.parts[mu]
+
+
+def test_reference_python_package_imports_on_gelib_base():
+    """With this repository's gelib_base on the path, GElib's own Python package imports unchanged and its host-side
+    pieces work through the C ABI: type calculus, random group elements, Wigner matrices.  Skipped where the reference
+    tree is not present (nothing here needs it at run time on a GPU box)."""
+    import os
+    import subprocess
+    import sys
+    import pytest
+    ref = "/root/reference/python/src"
+    if not os.path.isdir(os.path.join(ref, "gelib")):
+        pytest.skip("the GElib source tree is not present")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import torch, gelib, gelib_base\n"
+        "assert gelib_base.SO3part.view.__module__ == 'gelib_b200.backend'\n"
+        "v = gelib.SO3vec.randn(2, {0: 2, 1: 3, 2: 1})\n"
+        "tau = v.backend().get_tau().CGproduct(v.backend().get_tau(), 2).get_parts()\n"
+        "want = {}\n"
+        "t = {0: 2, 1: 3, 2: 1}\n"
+        "for l1, n1 in t.items():\n"
+        "    for l2, n2 in t.items():\n"
+        "        for l in range(abs(l1 - l2), min(l1 + l2, 2) + 1):\n"
+        "            want[l] = want.get(l, 0) + n1 * n2\n"
+        "assert tau == want, (tau, want)\n"
+        "R = gelib.SO3element.random()\n"
+        "assert torch.allclose(R @ R.t(), torch.eye(3), atol=1e-5)\n"
+        "D = gelib.SO3irrep(2).matrix(R)\n"
+        "assert torch.allclose(D @ D.conj().t(), torch.eye(5, dtype=torch.complex64), atol=1e-5)\n"
+        "x = gelib.SO3part.randn(2, 1, 3)\n"
+        "try:\n"
+        "    gelib.CGproduct(x, x, 1)\n"
+        "    raise SystemExit('a CPU product must raise: there is no CPU path')\n"
+        "except RuntimeError as e:\n"
+        "    assert 'CUDA' in str(e)\n"
+        "print('ok')\n")
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + ref)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
