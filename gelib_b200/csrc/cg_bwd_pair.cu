@@ -140,45 +140,72 @@ __device__ __forceinline__ void contract(const float (&G)[kGroupSlabs][2 * kCW],
 // G: the warp's quarter of the group's slabs; coef: the group's coefficient quads; o: the other operand's row chunk
 // for the first entry (4 x 16 bytes), ostep its signed step; a: the lane's slot in the warp's private accumulator
 // row of the first entry, astep its signed step.
+// Shared-memory accesses by 32-bit address with the offset folded into the instruction: the band loop keeps three
+// address registers (coefficients, operand row, accumulator slot) and no 64-bit address arithmetic.  They are
+// volatile, so they stay in program order: the loop below is written in the order it should issue.
+template <int OFF>
+__device__ __forceinline__ float4 lds128o(uint32_t a) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4+%5];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a), "n"(OFF));
+  return v;
+}
+__device__ __forceinline__ float2 lds64a(uint32_t a) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts64a(uint32_t a, float2 v) {
+  asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(a), "f"(v.x), "f"(v.y) : "memory");
+}
+
 struct BandEntry {
   float4 c, w[kCW / 2];
 };
-__device__ __forceinline__ void load_entry(BandEntry& e, const unsigned char* smem, int coef, int o) {
-  e.c = *reinterpret_cast<const float4*>(smem + coef);
-#pragma unroll
-  for (int t = 0; t < kCW / 2; t++) e.w[t] = *reinterpret_cast<const float4*>(smem + o + 16 * t);
+__device__ __forceinline__ void load_entry(BandEntry& e, uint32_t coef, uint32_t o) {
+  e.c = lds128o<0>(coef);
+  e.w[0] = lds128o<0>(o);
+  e.w[1] = lds128o<16>(o);
+  if (kCW > 4) {
+    e.w[kCW / 2 - 2] = lds128o<32>(o);
+    e.w[kCW / 2 - 1] = lds128o<48>(o);
+  }
 }
 template <int LM>
-__device__ __forceinline__ void use_entry(const float (&G)[kGroupSlabs][2 * kCW], const BandEntry& e, unsigned char* smem, int a) {
-  float2 s = *reinterpret_cast<float2*>(smem + a);
+__device__ __forceinline__ void use_entry(const float (&G)[kGroupSlabs][2 * kCW], const BandEntry& e, uint32_t a) {
+  float2 s = lds64a(a);
   float r, i;
   contract<LM>(G, e.c, e.w, r, i);
   s.x += r;
   s.y += i;
-  *reinterpret_cast<float2*>(smem + a) = s;
+  sts64a(a, s);
 }
+// The band of one group for one warp.  The loads of entry k+1 are issued before the arithmetic of entry k (two
+// register sets, used alternately).  All positions are 32-bit shared-memory addresses.
+// G: the warp's quarter of the group's slabs; coef: the group's coefficient quads; o: the other operand's row chunk
+// for the first entry, ostep its signed step in bytes; a: the lane's slot in the warp's private accumulator row of the
+// first entry, astep its signed step.
 template <int LM>
-__device__ __forceinline__ void band_loop(const float (&G)[kGroupSlabs][2 * kCW], unsigned char* smem, int coef, int cnt, int o,
-                                          int ostep, int a, int astep) {
+__device__ __forceinline__ void band_loop(const float (&G)[kGroupSlabs][2 * kCW], uint32_t coef, int cnt, uint32_t o, int ostep,
+                                          uint32_t a, int astep) {
   BandEntry A, B;
-  load_entry(A, smem, coef, o);
+  load_entry(A, coef, o);
   int k = 0;
   for (; k + 2 < cnt; k += 2) {
-    load_entry(B, smem, coef + 16, o + ostep);
-    use_entry<LM>(G, A, smem, a);
+    load_entry(B, coef + 16, o + ostep);
+    use_entry<LM>(G, A, a);
     coef += 32;
     o += 2 * ostep;
-    load_entry(A, smem, coef, o);
-    use_entry<LM>(G, B, smem, a + astep);
+    load_entry(A, coef, o);
+    use_entry<LM>(G, B, a + astep);
     a += 2 * astep;
   }
   // one or two entries are left, the first of them loaded
   if (k + 1 < cnt) {
-    load_entry(B, smem, coef + 16, o + ostep);
-    use_entry<LM>(G, A, smem, a);
-    use_entry<LM>(G, B, smem, a + astep);
+    load_entry(B, coef + 16, o + ostep);
+    use_entry<LM>(G, A, a);
+    use_entry<LM>(G, B, a + astep);
   } else {
-    use_entry<LM>(G, A, smem, a);
+    use_entry<LM>(G, A, a);
   }
 }
 
@@ -359,13 +386,13 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
             }
           }
         }
-        const int sb = ring_off + st * kStageBytes;
-        const int o = d0.y + q * (8 * kCW), a = mine_off + d0.w;
+        const uint32_t s0 = smem_u32(smem_raw), cf = s0 + ring_off + st * kStageBytes + kCoefOff;
+        const uint32_t o = s0 + d0.y + q * (8 * kCW), a = s0 + mine_off + d0.w;
         switch (nslab) {
-          case 1: band_loop<1>(G, smem_raw, sb + kCoefOff, cnt, o, d0.z, a, d1.x); break;
-          case 2: band_loop<2>(G, smem_raw, sb + kCoefOff, cnt, o, d0.z, a, d1.x); break;
-          case 3: band_loop<3>(G, smem_raw, sb + kCoefOff, cnt, o, d0.z, a, d1.x); break;
-          default: band_loop<4>(G, smem_raw, sb + kCoefOff, cnt, o, d0.z, a, d1.x); break;
+          case 1: band_loop<1>(G, cf, cnt, o, d0.z, a, d1.x); break;
+          case 2: band_loop<2>(G, cf, cnt, o, d0.z, a, d1.x); break;
+          case 3: band_loop<3>(G, cf, cnt, o, d0.z, a, d1.x); break;
+          default: band_loop<4>(G, cf, cnt, o, d0.z, a, d1.x); break;
         }
         if (d0.x & 0x10000) {  // last group of the pair-tile: the warp's partial rows go to the CTA's accumulators
           const int rows = (d0.x >> 24) & 0xff;
