@@ -93,9 +93,29 @@ __device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// Packed single precision (two lanes of one 64-bit register per instruction): the combination H = sum_l c_l G_l
+// takes one instruction per complex number and slab instead of two.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float a, float b) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
 // H = sum_l c_l G_l for the warp's 8 complex numbers, contracted with the conjugate of the other operand's 8.
 template <int LM>
-__device__ __forceinline__ void contract(const float (&G)[kGroupSlabs][2 * kCW], const float4 c, const float4 (&w)[kCW / 2], float& sr,
+__device__ __forceinline__ void contract(const f32x2 (&G)[kGroupSlabs][kCW], const float4 c, const float4 (&w)[kCW / 2], float& sr,
                                          float& si) {
   float v[2 * kCW];
 #pragma unroll
@@ -103,17 +123,19 @@ __device__ __forceinline__ void contract(const float (&G)[kGroupSlabs][2 * kCW],
     v[4 * t] = w[t].x; v[4 * t + 1] = w[t].y; v[4 * t + 2] = w[t].z; v[4 * t + 3] = w[t].w;
   }
   float H[2 * kCW];
+  const f32x2 c0 = pack2(c.x, c.x), c1 = pack2(c.y, c.y), c2 = pack2(c.z, c.z), c3 = pack2(c.w, c.w);
 #pragma unroll
-  for (int e = 0; e < 2 * kCW; e++) {
+  for (int j = 0; j < kCW; j++) {
+    f32x2 h;
     if (LM == 1) {
-      H[e] = G[0][e];
+      h = G[0][j];
     } else {
-      float h = c.x * G[0][e];
-      h = fmaf(c.y, G[1][e], h);
-      if (LM > 2) h = fmaf(c.z, G[2][e], h);
-      if (LM > 3) h = fmaf(c.w, G[3][e], h);
-      H[e] = h;
+      h = mul2(c0, G[0][j]);
+      h = fma2(c1, G[1][j], h);
+      if (LM > 2) h = fma2(c2, G[2][j], h);
+      if (LM > 3) h = fma2(c3, G[3][j], h);
     }
+    unpack2(h, H[2 * j], H[2 * j + 1]);
   }
   float sr0 = 0.f, si0 = 0.f, sr1 = 0.f, si1 = 0.f;
 #pragma unroll
@@ -171,7 +193,7 @@ __device__ __forceinline__ void load_entry(BandEntry& e, uint32_t coef, uint32_t
   }
 }
 template <int LM>
-__device__ __forceinline__ void use_entry(const float (&G)[kGroupSlabs][2 * kCW], const BandEntry& e, uint32_t a) {
+__device__ __forceinline__ void use_entry(const f32x2 (&G)[kGroupSlabs][kCW], const BandEntry& e, uint32_t a) {
   float2 s = lds64a(a);
   float r, i;
   contract<LM>(G, e.c, e.w, r, i);
@@ -185,7 +207,7 @@ __device__ __forceinline__ void use_entry(const float (&G)[kGroupSlabs][2 * kCW]
 // for the first entry, ostep its signed step in bytes; a: the lane's slot in the warp's private accumulator row of the
 // first entry, astep its signed step.
 template <int LM>
-__device__ __forceinline__ void band_loop(const float (&G)[kGroupSlabs][2 * kCW], uint32_t coef, int cnt, uint32_t o, int ostep,
+__device__ __forceinline__ void band_loop(const f32x2 (&G)[kGroupSlabs][kCW], uint32_t coef, int cnt, uint32_t o, int ostep,
                                           uint32_t a, int astep) {
   BandEntry A, B;
   load_entry(A, coef, o);
@@ -321,7 +343,9 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
             const uint32_t dst = sbase + s * kSlotBytes + rowi * kRowPitch + cc * 16;
             const long long step = 4LL * n2;  // two rows of the part, in floats
 #pragma unroll
+#ifndef ABL_NOCOPY
             for (int it = 0; it < 16 / kProducers; it++) cp_async16(dst + it * 2 * kRowPitch, src + it * step);
+#endif
           }
         }
       }
@@ -360,16 +384,16 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
         const int4 d0 = *reinterpret_cast<const int4*>(sbase + kDescOff + role * 32);
         const int4 d1 = *reinterpret_cast<const int4*>(sbase + kDescOff + role * 32 + 16);
         const int nslab = d0.x & 7, cnt = (d0.x >> 8) & 0xff;
-        float G[kGroupSlabs][2 * kCW];
+        f32x2 G[kGroupSlabs][kCW];
         if (role == 0) {
 #pragma unroll
           for (int s = 0; s < kGroupSlabs; s++) {
             if (s < nslab) {
-              const float4* gp = reinterpret_cast<const float4*>(sbase + s * kSlotBytes + goffs);
+              const ulonglong2* gp = reinterpret_cast<const ulonglong2*>(sbase + s * kSlotBytes + goffs);
 #pragma unroll
               for (int t = 0; t < kCW / 2; t++) {
-                const float4 w = gp[t];
-                G[s][4 * t] = w.x; G[s][4 * t + 1] = w.y; G[s][4 * t + 2] = w.z; G[s][4 * t + 3] = w.w;
+                const ulonglong2 w = gp[t];
+                G[s][2 * t] = w.x; G[s][2 * t + 1] = w.y;
               }
             }
           }
@@ -380,8 +404,7 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
               const unsigned char* gp = sbase + s * kSlotBytes + goffs;
 #pragma unroll
               for (int r = 0; r < kCW; r++) {
-                const float2 w = *reinterpret_cast<const float2*>(gp + r * kRowPitch);
-                G[s][2 * r] = w.x; G[s][2 * r + 1] = w.y;
+                G[s][r] = *reinterpret_cast<const f32x2*>(gp + r * kRowPitch);
               }
             }
           }
