@@ -32,10 +32,13 @@
 // Every wait on an mbarrier is bounded; on a timeout the kernel records it in a host-mapped status word, leaves its
 // loops, lets its copies in flight land, and returns; the C ABI reports the failure on the next call.
 #include <algorithm>
+#include <array>
 #include <cstdlib>
 #include <cstring>
 #include <map>
 #include <string>
+
+#include <cuda.h>
 
 #include "plan.h"
 #include "tc_common.h"
@@ -49,19 +52,31 @@ using namespace tc;
 constexpr int kSplit = 4;                            // warps per role: each takes 32 / kSplit of the other channel index (8 was tried: 19.7 ms)
 constexpr int kCW = 32 / kSplit;                     // complex numbers per lane and slab
 constexpr int kConsumers = 2 * kSplit;
-constexpr int kProducers = 4;                        // copy warps, one per scheduler; each moves a quarter of every slab
-constexpr int kThreads = (kConsumers + kProducers) * 32;
-constexpr int kRowPitch = 272;                       // bytes per staged slab row: 32 complex + 16
-constexpr int kSlotBytes = 32 * kRowPitch;           // one slab
 constexpr int kGroupSlabs = 4;                       // slabs per group
 constexpr int kMaxBand = 17;                         // band entries per group: 2*8+1
-constexpr int kCoefOff = kGroupSlabs * kSlotBytes;   // one coefficient quad per band entry
-constexpr int kDescOff = kCoefOff + kMaxBand * 16;   // the two consumer descriptors (32 bytes each)
-constexpr int kStageBytes = kDescOff + 64 + 48;      // 128 | size
 constexpr int kMaxStages = 4;
-constexpr int kHeaderBytes = 512;                    // mbarriers, cell offsets
+constexpr int kHeaderBytes = 768;                    // mbarriers, cell offsets, cell coordinates of the tensor maps
 constexpr int kRec = 7;                              // int4 per group record
-static_assert(kStageBytes % 128 == 0, "stages stay 128-byte aligned");
+constexpr int kMaxMaps = 16;                         // tensor maps per call: one per (g part, N2)
+
+// A stage of the ring: the group's slabs, one coefficient quad per band entry, the two consumer descriptors
+// (32 bytes each).  Two ways to fill it:
+//   kTma = true   one thread issues two tensor copies (cp.async.bulk.tensor, 32 rows x 128 bytes, 128-byte swizzle)
+//                 per slab and two bulk copies for coefficients and descriptors; a slab is 8192 bytes and a row's
+//                 16-byte chunk c sits at chunk c ^ (row & 7) of its half row, so both read patterns are
+//                 conflict-free without padding;
+//   kTma = false  four warps issue 16-byte cp.async; slab rows are padded to 272 bytes.  For views whose strides
+//                 or cell grid a five-dimensional tensor map cannot describe.
+template <bool kTma>
+struct Stage {
+  static constexpr int kRowPitch = kTma ? 256 : 272;
+  static constexpr int kSlotBytes = 32 * kRowPitch;
+  static constexpr int kCoefOff = kGroupSlabs * kSlotBytes;
+  static constexpr int kDescOff = kCoefOff + kMaxBand * 16;
+  static constexpr int kBytes = (kDescOff + 64 + 1023) / 1024 * 1024;
+  static constexpr int kProducers = kTma ? 1 : 4;    // copy warps
+  static constexpr int kThreads = (kConsumers + kProducers) * 32;
+};
 
 struct PairArgs {
   PartView x[kMaxParts], y[kMaxParts], g[kMaxParts], xg[kMaxParts], yg[kMaxParts];
@@ -76,13 +91,14 @@ struct PairArgs {
   //    its signed step in bytes, byte offset of the first entry's row in a warp's private rows, its step (+-256),
   //    float offset of the pair-tile's rows in the CTA accumulators, their pitch in floats, 0}
   // [4..6] for the producer:
-  //   {nslab | band length<<8 | n2<<16, index of the first coefficient quad, 4 x {ri | (m+l)<<8, first channel of the
-  //    tile inside part ri}, 0, 0}
+  //   {nslab | band length<<8 | n2<<16, index of the first coefficient quad, 4 x {ri | (m+l)<<8 | map<<16 | colblk<<21,
+  //    c1}, 0, 0}: the tile's first channel inside part ri is c1 * n2 + 32 * colblk
   const int4* recs;
   int ngroups;
   const float4* coef;                    // per band entry the coefficients of the group's slabs, zero-padded to 4
   int offs_extra;
   int do_x, do_y, x_atomic, y_atomic;
+  unsigned tk[kMaxParts][6];             // tensor maps: (cell dim A, cell dim B) = (b, g0, g1) x these multipliers
   int skip_group;                        // test hook: the producer never signals this group (-1: none)
   int* status;                           // host-mapped; set to 1 when a wait ran out
 };
@@ -267,31 +283,70 @@ __device__ __forceinline__ void flush_rows(const float* acc_cell, const PartView
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_constant__ PairArgs A, const int J) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
+// One tensor copy: 32 rows x 128 bytes of a slab (rank-5 map; the box is 32 x 32 x 1 x 1 x 1 floats).
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const void* map, int c0, int c1, int c2, int c3, int c4, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar)
+      : "memory");
+}
+// A bulk copy of `bytes` (a multiple of 16, both addresses 16-byte aligned) that completes on the mbarrier.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+struct TmaMaps {
+  CUtensorMap m[kMaxMaps];
+};
+
+template <bool kTma>
+__global__ void __launch_bounds__(Stage<kTma>::kThreads, 1)
+    cg_bwd_pair_kernel(const __grid_constant__ PairArgs A, const __grid_constant__ TmaMaps M, const int J) {
+  using S = Stage<kTma>;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw);           // [kMaxStages]
   uint64_t* empty = full + kMaxStages;                               // [kMaxStages]
   long long* goff = reinterpret_cast<long long*>(smem_raw + 128);    // [kMaxParts] cell offsets into the g parts
   long long* xgoff = goff + kMaxParts;
   long long* ygoff = xgoff + kMaxParts;
+  int* tcoord = reinterpret_cast<int*>(smem_raw + 512);              // [kMaxParts][2] the cell's coordinates in the maps
   float* stage_f = reinterpret_cast<float*>(smem_raw + kHeaderBytes);   // staged x,y rows of the cell
   float* acc_f = stage_f + A.cell_floats;                               // gradient accumulators, same layout
   float2* priv = reinterpret_cast<float2*>(acc_f + A.cell_floats);      // [kConsumers][J][32] private partial rows
-  const int ring_off = (kHeaderBytes + 8 * A.cell_floats + kConsumers * J * 256 + 127) & ~127;
+  const int ring_off = (kHeaderBytes + 8 * A.cell_floats + kConsumers * J * 256 + 1023) & ~1023;
   unsigned char* ring = smem_raw + ring_off;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long cell = blockIdx.x;
   const int NS = A.nstages;
 
+  if (kTma && (smem_u32(smem_raw) & 1023u) != 0) {  // the swizzle pattern is a function of the address
+    if (threadIdx.x == 0) *A.status = 1;
+    return;
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < NS; s++) {
-      mbar_init(&full[s], 32 * kProducers);  // one arrival per producer lane, when that lane's copies have landed
+      // tensor copies: one arrival, by the thread that states the bytes to come; cp.async: one per producer lane
+      mbar_init(&full[s], kTma ? 1 : 32 * S::kProducers);
       mbar_init(&empty[s], kConsumers);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   for (int e = threadIdx.x; e < A.ng; e += blockDim.x) goff[e] = cell_offset(A.g[e], A.cg, cell);
+  if (kTma) {
+    for (int e = threadIdx.x; e < A.ng; e += blockDim.x) {
+      const unsigned c = (unsigned)cell;
+      const unsigned g1 = c % (unsigned)A.cg.G1, t = c / (unsigned)A.cg.G1;
+      const unsigned g0 = t % (unsigned)A.cg.G0, b = t / (unsigned)A.cg.G0;
+      tcoord[2 * e] = (int)(b * A.tk[e][0] + g0 * A.tk[e][1] + g1 * A.tk[e][2]);
+      tcoord[2 * e + 1] = (int)(b * A.tk[e][3] + g0 * A.tk[e][4] + g1 * A.tk[e][5]);
+    }
+  }
   if (A.do_x)
     for (int e = threadIdx.x; e < A.nx; e += blockDim.x) xgoff[e] = cell_offset(A.xg[e], A.cg, cell);
   if (A.do_y)
@@ -302,8 +357,7 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
   __syncthreads();
 
   if (warp >= kConsumers) {
-    // ---- producers: 16-byte asynchronous copies, a group per stage.  Lane t moves chunk t of two rows at a time
-    // (global reads of 512 contiguous bytes per instruction); a slab takes 16 such instructions, four per warp.
+    // ---- producers: a group per stage
     const int pw = warp - kConsumers;
     bool ok = true;
     // Records are fetched 32 groups at a time, one group per lane, a batch ahead of their use, and handed round
@@ -314,6 +368,8 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
     };
     int4 b0 = make_int4(0, 0, 0, 0), b1 = b0, b2 = b0, nb0 = b0, nb1 = b0, nb2 = b0;
     if (A.ngroups > 0) fetch(lane, b0, b1, b2);
+    // cp.async: lane t moves chunk t of two rows at a time (global reads of 512 contiguous bytes per instruction);
+    // a slab takes 16 such instructions, four per warp
     const int rowi = 8 * pw + (lane >> 4), cc = lane & 15;   // first row this lane copies, and its 16-byte chunk
     const uint32_t ring_a = smem_u32(ring);
     int st = 0, phase = 0;
@@ -330,30 +386,47 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
       if (!first_round) ok = mbar_wait(&empty[st], phase ^ 1);
       if (!ok) break;
       const int nslab = p0.x & 7, cnt = (p0.x >> 8) & 0xff, n2 = (p0.x >> 16) & 0xffff;
-      const uint32_t sbase = ring_a + st * kStageBytes;
+      const uint32_t sbase = ring_a + st * S::kBytes;
       const int sw[8] = {p0.z, p0.w, p1.x, p1.y, p1.z, p1.w, p2.x, p2.y};
-      {
+      if (kTma) {
+        if (lane == 0 && gi != A.skip_group) {
+          const uint32_t bar = smem_u32(&full[st]);
+          mbar_arrive_expect(bar, (uint32_t)(nslab * S::kSlotBytes + 64 + cnt * 16));
+#pragma unroll
+          for (int s = 0; s < kGroupSlabs; s++) {
+            if (s < nslab) {
+              const unsigned w = (unsigned)sw[2 * s];
+              const int ri = w & 0xff, row = (w >> 8) & 0xff, slot = (w >> 16) & 0x1f, col = (int)(w >> 21) * 64;
+              const int ca = tcoord[2 * ri], cb = tcoord[2 * ri + 1];
+              tma_load_5d(sbase + s * S::kSlotBytes, &M.m[slot], col, sw[2 * s + 1], row, cb, ca, bar);
+              tma_load_5d(sbase + s * S::kSlotBytes + 4096, &M.m[slot], col + 32, sw[2 * s + 1], row, cb, ca, bar);
+            }
+          }
+          bulk_load(sbase + S::kCoefOff, A.coef + p0.y, (uint32_t)cnt * 16, bar);
+          bulk_load(sbase + S::kDescOff, &A.recs[kRec * gi], 64, bar);
+        }
+      } else {
 #pragma unroll
         for (int s = 0; s < kGroupSlabs; s++) {
           if (s < nslab) {
-            const int ri = sw[2 * s] & 0xff, row = sw[2 * s] >> 8;
+            const unsigned w = (unsigned)sw[2 * s];
+            const int ri = w & 0xff, row = (w >> 8) & 0xff;
+            const long long off = (long long)sw[2 * s + 1] * n2 + (int)(w >> 21) * 32;   // first channel of the tile
             const PartView& gp = A.g[ri];
             const float* src = gp.base + goff[ri] + (long long)row * gp.sm +
-                               2LL * ((long long)sw[2 * s + 1] + A.offs_extra + (long long)rowi * n2) + 4 * cc;
-            const uint32_t dst = sbase + s * kSlotBytes + rowi * kRowPitch + cc * 16;
+                               2LL * (off + A.offs_extra + (long long)rowi * n2) + 4 * cc;
+            const uint32_t dst = sbase + s * S::kSlotBytes + rowi * S::kRowPitch + cc * 16;
             const long long step = 4LL * n2;  // two rows of the part, in floats
 #pragma unroll
-#ifndef ABL_NOCOPY
-            for (int it = 0; it < 16 / kProducers; it++) cp_async16(dst + it * 2 * kRowPitch, src + it * step);
-#endif
+            for (int it = 0; it < 4; it++) cp_async16(dst + it * 2 * S::kRowPitch, src + it * step);
           }
         }
+        if (pw == 0) {
+          if (lane < cnt) cp_async16(sbase + S::kCoefOff + lane * 16, A.coef + p0.y + lane);
+          if (lane < 4) cp_async16(sbase + S::kDescOff + lane * 16, &A.recs[kRec * gi + lane]);
+        }
+        if (gi != A.skip_group) cp_async_arrive(&full[st]);
       }
-      if (pw == 0) {
-        if (lane < cnt) cp_async16(sbase + kCoefOff + lane * 16, A.coef + p0.y + lane);
-        if (lane < 4) cp_async16(sbase + kDescOff + lane * 16, &A.recs[kRec * gi + lane]);
-      }
-      if (gi != A.skip_group) cp_async_arrive(&full[st]);
       if (++st == NS) {
         st = 0;
         phase ^= 1;
@@ -363,7 +436,7 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
         b0 = nb0; b1 = nb1; b2 = nb2;
       }
     }
-    cp_async_wait_all();  // nothing of this warp is in flight when the CTA gives its shared memory back
+    if (!kTma) cp_async_wait_all();  // nothing of this warp is in flight when the CTA gives its shared memory back
     if (!ok && lane == 0) *A.status = 1;
   } else {
     // ---- consumers
@@ -371,28 +444,36 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
     const bool active = role == 0 ? (A.do_x != 0) : (A.do_y != 0);
     float2* mine = priv + (warp * J) * 32 + lane;
     const int mine_off = kHeaderBytes + 8 * A.cell_floats + (warp * J * 32 + lane) * 8;  // the same as a byte offset
-    // where the warp's quarter of a slab sits inside a slot: xg warps read row `lane`, columns 8q..8q+7 (16-byte
-    // loads, lanes 272 bytes apart); yg warps read rows 8q..8q+7, column `lane` (8-byte loads, lanes adjacent)
-    const int goffs = role == 0 ? lane * kRowPitch + q * (8 * kCW) : kCW * q * kRowPitch + lane * 8;
+    // Where the warp's quarter of a slab sits inside a slot.  xg warps read row `lane`, columns 8q..8q+7, as four
+    // 16-byte chunks; yg warps read rows 8q..8q+7, column `lane`, as eight 8-byte loads (lanes adjacent).
+    int goffs[kCW];
+#pragma unroll
+    for (int t = 0; t < kCW; t++) {
+      if (kTma) {
+        goffs[t] = role == 0 ? (q >> 1) * 4096 + lane * 128 + ((((q & 1) * 4 + (t & 3)) ^ (lane & 7)) << 4)
+                             : (lane >> 4) * 4096 + (kCW * q + t) * 128 + (((((lane & 15) >> 1) ^ t) & 7) << 4) + (lane & 1) * 8;
+      } else {
+        goffs[t] = role == 0 ? lane * S::kRowPitch + q * (8 * kCW) + (t & 3) * 16 : (kCW * q + t) * S::kRowPitch + lane * 8;
+      }
+    }
     bool ok = true;
     int st = 0, phase = 0;
     for (int gi = 0; gi < A.ngroups; gi++) {
       ok = mbar_wait(&full[st], phase);
       if (!ok) break;
       if (active) {
-        const unsigned char* sbase = ring + st * kStageBytes;
-        const int4 d0 = *reinterpret_cast<const int4*>(sbase + kDescOff + role * 32);
-        const int4 d1 = *reinterpret_cast<const int4*>(sbase + kDescOff + role * 32 + 16);
+        const unsigned char* sbase = ring + st * S::kBytes;
+        const int4 d0 = *reinterpret_cast<const int4*>(sbase + S::kDescOff + role * 32);
+        const int4 d1 = *reinterpret_cast<const int4*>(sbase + S::kDescOff + role * 32 + 16);
         const int nslab = d0.x & 7, cnt = (d0.x >> 8) & 0xff;
         f32x2 G[kGroupSlabs][kCW];
         if (role == 0) {
 #pragma unroll
           for (int s = 0; s < kGroupSlabs; s++) {
             if (s < nslab) {
-              const ulonglong2* gp = reinterpret_cast<const ulonglong2*>(sbase + s * kSlotBytes + goffs);
 #pragma unroll
               for (int t = 0; t < kCW / 2; t++) {
-                const ulonglong2 w = gp[t];
+                const ulonglong2 w = *reinterpret_cast<const ulonglong2*>(sbase + s * S::kSlotBytes + goffs[t]);
                 G[s][2 * t] = w.x; G[s][2 * t + 1] = w.y;
               }
             }
@@ -401,15 +482,12 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
 #pragma unroll
           for (int s = 0; s < kGroupSlabs; s++) {
             if (s < nslab) {
-              const unsigned char* gp = sbase + s * kSlotBytes + goffs;
 #pragma unroll
-              for (int r = 0; r < kCW; r++) {
-                G[s][r] = *reinterpret_cast<const f32x2*>(gp + r * kRowPitch);
-              }
+              for (int r = 0; r < kCW; r++) G[s][r] = *reinterpret_cast<const f32x2*>(sbase + s * S::kSlotBytes + goffs[r]);
             }
           }
         }
-        const uint32_t s0 = smem_u32(smem_raw), cf = s0 + ring_off + st * kStageBytes + kCoefOff;
+        const uint32_t s0 = smem_u32(smem_raw), cf = s0 + ring_off + st * S::kBytes + S::kCoefOff;
         const uint32_t o = s0 + d0.y + q * (8 * kCW), a = s0 + mine_off + d0.w;
         switch (nslab) {
           case 1: band_loop<1>(G, cf, cnt, o, d0.z, a, d1.x); break;
@@ -441,6 +519,101 @@ __global__ void __launch_bounds__(kThreads, 1) cg_bwd_pair_kernel(const __grid_c
   __syncthreads();
   if (A.do_x) flush_rows(acc_f, A.xg, xgoff, A.xoff, A.nx, A.x_atomic != 0);
   if (A.do_y) flush_rows(acc_f, A.yg, ygoff, A.yoff, A.ny, A.y_atomic != 0);
+}
+
+}  // namespace
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      p = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// The tensor maps of one call: for every (g part, N2) of the plan a rank-5 view
+//   {2*N2 floats of a row of N2 channels, rows of N2 channels, m rows, inner cell dimension, outer cell dimension}
+// of the part, box 32 floats x 32 rows, 128-byte swizzle.  The cells (b, g0, g1) of the part become at most two
+// dimensions (extent-1 and broadcast dimensions drop out, neighbours that are contiguous merge).  False when the
+// views cannot be described that way (strides not multiples of 16 bytes, three independent cell dimensions, ...):
+// the caller then takes the cp.async producer.
+bool encode_maps(const VecCall& c, const std::vector<int>& info, PairArgs& a, TmaMaps& maps) {
+  if (info.size() < 2 || !info[0]) return false;
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return false;
+  const int nslots = info[1];
+  struct Dim {
+    unsigned long long ext;
+    long long stride;  // floats
+    unsigned k[3];
+  };
+  std::vector<std::array<Dim, 2>> cell_dims(c.r.size());
+  for (size_t ri = 0; ri < c.r.size(); ri++) {
+    const PartView& p = c.r[ri];
+    std::vector<Dim> L;
+    const long long ext[3] = {c.cg.B, c.cg.G0, c.cg.G1}, str[3] = {p.sb, p.sg0, p.sg1};
+    for (int i = 0; i < 3; i++) {
+      if (ext[i] <= 1 || str[i] == 0) continue;
+      if (str[i] < 0) return false;
+      Dim d = {(unsigned long long)ext[i], str[i], {0, 0, 0}};
+      d.k[i] = 1;
+      L.push_back(d);
+    }
+    while (L.size() > 2) {  // merge an outer dimension with its inner neighbour when they are contiguous
+      bool merged = false;
+      for (size_t i = 0; i + 1 < L.size() && !merged; i++) {
+        if (L[i].stride == (long long)L[i + 1].ext * L[i + 1].stride) {
+          Dim d = L[i + 1];
+          for (int j = 0; j < 3; j++) d.k[j] = L[i].k[j] * (unsigned)L[i + 1].ext + L[i + 1].k[j];
+          d.ext = L[i].ext * L[i + 1].ext;
+          L[i] = d;
+          L.erase(L.begin() + i + 1);
+          merged = true;
+        }
+      }
+      if (!merged) return false;
+    }
+    const Dim none = {1, 0, {0, 0, 0}};
+    cell_dims[ri][0] = L.size() == 2 ? L[0] : none;             // outer
+    cell_dims[ri][1] = L.empty() ? none : L.back();             // inner
+    for (int j = 0; j < 3; j++) {
+      a.tk[ri][j] = cell_dims[ri][0].k[j];
+      a.tk[ri][3 + j] = cell_dims[ri][1].k[j];
+    }
+  }
+  for (int sl = 0; sl < nslots; sl++) {
+    const int ri = info[2 + 3 * sl], n2 = info[3 + 3 * sl], rows = info[4 + 3 * sl];
+    const PartView& p = c.r[ri];
+    float* base = p.base + 2LL * c.offs_extra;
+    if (reinterpret_cast<uintptr_t>(base) % 16) return false;
+    cuuint64_t dims[5] = {(cuuint64_t)2 * n2, (cuuint64_t)rows, (cuuint64_t)(2 * p.l + 1), cell_dims[ri][1].ext, cell_dims[ri][0].ext};
+    long long str[4] = {(long long)n2 * 8, p.sm * 4, cell_dims[ri][1].stride * 4, cell_dims[ri][0].stride * 4};
+    cuuint64_t strides[4];
+    for (int i = 0; i < 4; i++) {
+      if (dims[i + 1] == 1) str[i] = i == 0 ? 16 : (long long)strides[i - 1] * (long long)dims[i];  // never used: any valid value
+      if (str[i] <= 0 || str[i] % 16 || str[i] >= (1LL << 40)) return false;
+      strides[i] = (cuuint64_t)str[i];
+    }
+    for (int i = 0; i < 5; i++)
+      if (dims[i] == 0 || dims[i] > 0xffffffffULL) return false;
+    const cuuint32_t box[5] = {32, 32, 1, 1, 1}, one[5] = {1, 1, 1, 1, 1};
+    if (enc(&maps.m[sl], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, base, dims, strides, box, one, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return false;
+  }
+  return true;
 }
 
 }  // namespace
@@ -479,12 +652,13 @@ int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s, int min_groups) {
   a.ny = (int)c.y.size();
   a.ng = (int)c.r.size();
   a.cell_floats = off;
-  const size_t fixed = ((size_t)kHeaderBytes + (size_t)8 * off + (size_t)kConsumers * J * 256 + 127) & ~(size_t)127;
-  int ns = kMaxStages;
-  while (ns >= 2 && fixed + (size_t)ns * kStageBytes > 227 * 1024) ns--;
-  if (ns < 2) return -1;
-  a.nstages = ns;
-  const size_t smem = fixed + (size_t)ns * kStageBytes;
+  const size_t fixed = ((size_t)kHeaderBytes + (size_t)8 * off + (size_t)kConsumers * J * 256 + 1023) & ~(size_t)1023;
+  auto stages_that_fit = [&](size_t stage_bytes) {
+    int ns = kMaxStages;
+    while (ns >= 2 && fixed + (size_t)ns * stage_bytes > 227 * 1024) ns--;
+    return ns;
+  };
+  if (stages_that_fit(Stage<false>::kBytes) < 2) return -1;
 
   std::vector<int> key = {10 /*family*/, (int)c.x.size(), (int)c.y.size(), (int)c.r.size()};
   for (const auto& p : c.x) { key.push_back(p.l); key.push_back(p.n); }
@@ -498,6 +672,10 @@ int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s, int min_groups) {
     std::map<std::pair<int, int>, std::vector<const Triple*>> pairs;
     for (const Triple& t : p.sched.triples) pairs[{t.xi, t.yi}].push_back(&t);
     std::vector<float>& quads = p.h_floats;
+    // tensor maps of a call: one per (g part, N2); h_jobs = {maps fit, number of maps, then per map: part, N2, rows}
+    std::map<std::pair<int, int>, int> slots;
+    std::vector<int> slot_rows;
+    bool maps_fit = true;
     for (const auto& kv : pairs) {
       const auto& ts = kv.second;
       const int xi = kv.first.first, yi = kv.first.second;
@@ -518,8 +696,20 @@ int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s, int min_groups) {
               int sw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
               for (int sidx = 0; sidx < nslab; sidx++) {
                 const Triple* t = act[c0 + sidx];
-                sw[2 * sidx] = t->ri | ((m + t->l) << 8);
-                sw[2 * sidx + 1] = t->offs + a0 * n2 + b0;
+                // the part's channels of one (cell, row) as a matrix with rows of n2: the tile starts at row c1,
+                // column 32 * colblk, and its 32 rows are 32 consecutive rows of that matrix
+                const int off = t->offs + a0 * n2 + b0, c1 = off / n2, colblk = (off % n2) / 32;
+                auto it = slots.find({t->ri, n2});
+                if (it == slots.end()) {
+                  it = slots.emplace(std::make_pair((int)t->ri, n2), (int)slots.size()).first;
+                  slot_rows.push_back(0);
+                }
+                const int slot = it->second;
+                if (slot >= kMaxMaps || colblk >= 1024) maps_fit = false;
+                slot_rows[slot] = std::max(slot_rows[slot], c1 + 32);
+                sw[2 * sidx] = (int)((unsigned)t->ri | ((unsigned)(m + t->l) << 8) | ((unsigned)(slot & 0x1f) << 16) |
+                                     ((unsigned)(colblk & 0x3ff) << 21));
+                sw[2 * sidx + 1] = c1;
               }
               const int head = nslab | (cnt << 8);
               // xg warps: y rows downwards from m2 = m - lo, accumulator rows upwards from m1 = lo
@@ -554,6 +744,14 @@ int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s, int min_groups) {
           }
         }
     }
+    p.h_jobs.assign(2 + 3 * slots.size(), 0);
+    p.h_jobs[0] = maps_fit ? 1 : 0;
+    p.h_jobs[1] = (int)slots.size();
+    for (const auto& kv : slots) {
+      p.h_jobs[2 + 3 * kv.second] = kv.first.first;
+      p.h_jobs[3 + 3 * kv.second] = kv.first.second;
+      p.h_jobs[4 + 3 * kv.second] = slot_rows[kv.second];
+    }
   });
   if (!plan) return GELIB_CUDA_ERROR;
   if (plan->nitems == 0 || c.cg.ncells == 0) return GELIB_OK;
@@ -572,10 +770,26 @@ int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s, int min_groups) {
   a.skip_group = inject_timeout() ? 0 : -1;
   a.status = status;
 
-  cudaError_t e = cudaFuncSetAttribute(cg_bwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e == cudaSuccess) {
-    cg_bwd_pair_kernel<<<(unsigned)c.cg.ncells, kThreads, smem, s>>>(a, J);
-    e = cudaGetLastError();
+  TmaMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  const bool tma = pair_tma() && encode_maps(c, plan->h_jobs, a, maps);
+  cudaError_t e;
+  if (tma) {
+    a.nstages = stages_that_fit(Stage<true>::kBytes);
+    const size_t smem = fixed + (size_t)a.nstages * Stage<true>::kBytes;
+    e = cudaFuncSetAttribute(cg_bwd_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) {
+      cg_bwd_pair_kernel<true><<<(unsigned)c.cg.ncells, Stage<true>::kThreads, smem, s>>>(a, maps, J);
+      e = cudaGetLastError();
+    }
+  } else {
+    a.nstages = stages_that_fit(Stage<false>::kBytes);
+    const size_t smem = fixed + (size_t)a.nstages * Stage<false>::kBytes;
+    e = cudaFuncSetAttribute(cg_bwd_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) {
+      cg_bwd_pair_kernel<false><<<(unsigned)c.cg.ncells, Stage<false>::kThreads, smem, s>>>(a, maps, J);
+      e = cudaGetLastError();
+    }
   }
   if (e != cudaSuccess) return check_cuda(e, fn, "pair backward kernel launch");
   count_launch();

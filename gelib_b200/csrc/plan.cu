@@ -37,7 +37,7 @@ bool upload(const std::vector<T>& h, T** d) {
 
 namespace {
 struct Options {
-  std::atomic<int> fwd{kFwdAuto}, bwd{kBwdAuto}, inject{0};
+  std::atomic<int> fwd{kFwdAuto}, bwd{kBwdAuto}, inject{0}, pair_tma{1};
 };
 int parse_fwd(const char* v) {
   if (!v || !*v || !strcmp(v, "auto")) return kFwdAuto;
@@ -64,6 +64,8 @@ Options& options() {
     o.bwd = b < 0 ? kBwdAuto : b;
     const char* inj = getenv("GELIB_B200_INJECT_TIMEOUT");
     o.inject = inj && atoi(inj) != 0;
+    const char* tma = getenv("GELIB_B200_PAIR_TMA");
+    o.pair_tma = !(tma && *tma && atoi(tma) == 0);
   });
   return o;
 }
@@ -72,6 +74,7 @@ Options& options() {
 int fwd_mode() { return options().fwd.load(std::memory_order_relaxed); }
 int bwd_mode() { return options().bwd.load(std::memory_order_relaxed); }
 bool inject_timeout() { return options().inject.load(std::memory_order_relaxed) != 0; }
+bool pair_tma() { return options().pair_tma.load(std::memory_order_relaxed) != 0; }
 
 int set_option(const char* name, const char* value) {
   if (!name) return GELIB_INVALID;
@@ -86,6 +89,10 @@ int set_option(const char* name, const char* value) {
     const int v = parse_bwd(value);
     if (v < 0) return GELIB_INVALID;
     o.bwd = v;
+    return GELIB_OK;
+  }
+  if (!strcmp(name, "pair_tma")) {
+    o.pair_tma = !(value && *value && atoi(value) == 0);
     return GELIB_OK;
   }
   if (!strcmp(name, "inject_timeout")) {

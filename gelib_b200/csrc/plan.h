@@ -61,6 +61,7 @@ enum FwdMode { kFwdAuto = 0, kFwdSimt, kFwdTc, kFwdTcStrict };
 enum BwdMode { kBwdAuto = 0, kBwdSimt, kBwdPair, kBwdPairStrict, kBwdTc, kBwdTcStrict };
 int fwd_mode();
 int bwd_mode();
+bool pair_tma();        // the pair backward kernel fills its ring with tensor copies when the views allow (default on)
 bool inject_timeout();  // tests only: make one bounded device wait run out (no fault is involved)
 int set_option(const char* name, const char* value);  // GELIB_OK or GELIB_INVALID
 
