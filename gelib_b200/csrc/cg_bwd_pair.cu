@@ -51,7 +51,7 @@ using namespace tc;
 
 constexpr int kSplit = 4;                            // warps per role: each takes 32 / kSplit of the other channel index (8 was tried: 19.7 ms)
 constexpr int kCW = 32 / kSplit;                     // complex numbers per lane and slab
-constexpr int kConsumers = 2 * kSplit;
+constexpr int kSetWarps = 2 * kSplit;                // warps that share a group: two roles x kSplit
 constexpr int kGroupSlabs = 4;                       // slabs per group
 constexpr int kMaxBand = 17;                         // band entries per group: 2*8+1
 constexpr int kMaxStages = 4;
@@ -75,7 +75,15 @@ struct Stage {
   static constexpr int kDescOff = kCoefOff + kMaxBand * 16;
   static constexpr int kBytes = (kDescOff + 64 + 1023) / 1024 * 1024;
   static constexpr int kProducers = kTma ? 1 : 4;    // copy warps
+  // Sets of consumer warps; set s takes the groups with index = s mod kSets.  The copy warps of the cp.async
+  // variant leave registers for one set only.
+#ifndef PAIR_SETS
+#define PAIR_SETS 1
+#endif
+  static constexpr int kSets = kTma ? PAIR_SETS : 1;
+  static constexpr int kConsumers = kSets * kSetWarps;
   static constexpr int kThreads = (kConsumers + kProducers) * 32;
+  static constexpr int kMaxRegs = kTma && kSets == 2 ? 96 : 168;  // a scheduler's 16384 registers / its warps, in steps of 8
 };
 
 struct PairArgs {
@@ -261,26 +269,9 @@ __device__ __forceinline__ void stage_parts(float* dst_cell, const PartView* par
   }
 }
 
-__device__ __forceinline__ void flush_rows(const float* acc_cell, const PartView* out, const long long* cell_off,
-                                           const int* off, int nparts, bool atomic) {
-  for (int i = 0; i < nparts; i++) {
-    const PartView& p = out[i];
-    const int n = p.n, total = (2 * p.l + 1) * n;
-    for (int e = threadIdx.x; e < total; e += blockDim.x) {
-      const int row = e / n, ch = e - row * n;
-      const float2 v = *reinterpret_cast<const float2*>(acc_cell + off[i] + 2 * e);
-      float* dst = p.base + cell_off[i] + (long long)row * p.sm + 2 * ch;
-      if (atomic) {
-        atomicAdd(dst, v.x);
-        atomicAdd(dst + 1, v.y);
-      } else {
-        float2 o = *reinterpret_cast<float2*>(dst);
-        o.x += v.x;
-        o.y += v.y;
-        *reinterpret_cast<float2*>(dst) = o;
-      }
-    }
-  }
+// One complex number added to global memory without a return value.
+__device__ __forceinline__ void red_add2(float* dst, float2 v) {
+  asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(__cvta_generic_to_global(dst)), "f"(v.x), "f"(v.y) : "memory");
 }
 
 // One tensor copy: 32 rows x 128 bytes of a slab (rank-5 map; the box is 32 x 32 x 1 x 1 x 1 floats).
@@ -305,9 +296,10 @@ struct TmaMaps {
 };
 
 template <bool kTma>
-__global__ void __launch_bounds__(Stage<kTma>::kThreads, 1)
+__global__ void __maxnreg__(Stage<kTma>::kMaxRegs)
     cg_bwd_pair_kernel(const __grid_constant__ PairArgs A, const __grid_constant__ TmaMaps M, const int J) {
   using S = Stage<kTma>;
+  constexpr int kConsumers = S::kConsumers;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw);           // [kMaxStages]
   uint64_t* empty = full + kMaxStages;                               // [kMaxStages]
@@ -316,9 +308,8 @@ __global__ void __launch_bounds__(Stage<kTma>::kThreads, 1)
   long long* ygoff = xgoff + kMaxParts;
   int* tcoord = reinterpret_cast<int*>(smem_raw + 512);              // [kMaxParts][2] the cell's coordinates in the maps
   float* stage_f = reinterpret_cast<float*>(smem_raw + kHeaderBytes);   // staged x,y rows of the cell
-  float* acc_f = stage_f + A.cell_floats;                               // gradient accumulators, same layout
-  float2* priv = reinterpret_cast<float2*>(acc_f + A.cell_floats);      // [kConsumers][J][32] private partial rows
-  const int ring_off = (kHeaderBytes + 8 * A.cell_floats + kConsumers * J * 256 + 1023) & ~1023;
+  float2* priv = reinterpret_cast<float2*>(stage_f + A.cell_floats);    // [kConsumers][J][32] private partial rows
+  const int ring_off = (kHeaderBytes + 4 * A.cell_floats + kConsumers * J * 256 + 1023) & ~1023;
   unsigned char* ring = smem_raw + ring_off;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -333,7 +324,7 @@ __global__ void __launch_bounds__(Stage<kTma>::kThreads, 1)
     for (int s = 0; s < NS; s++) {
       // tensor copies: one arrival, by the thread that states the bytes to come; cp.async: one per producer lane
       mbar_init(&full[s], kTma ? 1 : 32 * S::kProducers);
-      mbar_init(&empty[s], kConsumers);
+      mbar_init(&empty[s], kSetWarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -353,7 +344,7 @@ __global__ void __launch_bounds__(Stage<kTma>::kThreads, 1)
     for (int e = threadIdx.x; e < A.ny; e += blockDim.x) ygoff[e] = cell_offset(A.yg[e], A.cg, cell);
   stage_parts(stage_f, A.x, A.xoff, A.nx, A.cg, cell);
   stage_parts(stage_f, A.y, A.yoff, A.ny, A.cg, cell);
-  for (int e = threadIdx.x; e < A.cell_floats + kConsumers * J * 64; e += blockDim.x) acc_f[e] = 0.f;  // + priv
+  for (int e = threadIdx.x; e < kConsumers * J * 32; e += blockDim.x) priv[e] = make_float2(0.f, 0.f);
   __syncthreads();
 
   if (warp >= kConsumers) {
@@ -440,10 +431,13 @@ __global__ void __launch_bounds__(Stage<kTma>::kThreads, 1)
     if (!ok && lane == 0) *A.status = 1;
   } else {
     // ---- consumers
-    const int role = warp / kSplit, q = warp % kSplit;
+    const int set = warp / kSetWarps, role = (warp % kSetWarps) / kSplit, q = warp % kSplit;
     const bool active = role == 0 ? (A.do_x != 0) : (A.do_y != 0);
     float2* mine = priv + (warp * J) * 32 + lane;
-    const int mine_off = kHeaderBytes + 8 * A.cell_floats + (warp * J * 32 + lane) * 8;  // the same as a byte offset
+    const int mine_off = kHeaderBytes + 4 * A.cell_floats + (warp * J * 32 + lane) * 8;  // the same as a byte offset
+    const PartView* outs = role == 0 ? A.xg : A.yg;
+    const long long* outoff = role == 0 ? xgoff : ygoff;
+    const int last_bit = S::kSets == 1 ? 0x10000 : 0x20000;
     // Where the warp's quarter of a slab sits inside a slot.  xg warps read row `lane`, columns 8q..8q+7, as four
     // 16-byte chunks; yg warps read rows 8q..8q+7, column `lane`, as eight 8-byte loads (lanes adjacent).
     int goffs[kCW];
@@ -457,8 +451,8 @@ __global__ void __launch_bounds__(Stage<kTma>::kThreads, 1)
       }
     }
     bool ok = true;
-    int st = 0, phase = 0;
-    for (int gi = 0; gi < A.ngroups; gi++) {
+    int st = set % NS, phase = (set / NS) & 1;
+    for (int gi = set; gi < A.ngroups; gi += S::kSets) {
       ok = mbar_wait(&full[st], phase);
       if (!ok) break;
       if (active) {
@@ -495,30 +489,27 @@ __global__ void __launch_bounds__(Stage<kTma>::kThreads, 1)
           case 3: band_loop<3>(G, cf, cnt, o, d0.z, a, d1.x); break;
           default: band_loop<4>(G, cf, cnt, o, d0.z, a, d1.x); break;
         }
-        if (d0.x & 0x10000) {  // last group of the pair-tile: the warp's partial rows go to the CTA's accumulators
+        if (d0.x & last_bit) {  // the set's last group of the pair-tile: the warp's partial rows go to global memory
           const int rows = (d0.x >> 24) & 0xff;
-          float* dst = acc_f + d1.y + 2 * lane;
+          const PartView& op = outs[d1.y];
+          float* dst = op.base + outoff[d1.y] + d1.z + 2 * lane;
           for (int j = 0; j < rows; j++) {
             const float2 v = mine[j * 32];
             mine[j * 32] = make_float2(0.f, 0.f);
-            atomicAdd(dst + j * d1.z, v.x);
-            atomicAdd(dst + j * d1.z + 1, v.y);
+            red_add2(dst + j * op.sm, v);
           }
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[st]);  // the stage (slabs, coefficients, descriptors) is free again
-      if (++st == NS) {
-        st = 0;
+      st += S::kSets;
+      if (st >= NS) {  // NS >= kSets
+        st -= NS;
         phase ^= 1;
       }
     }
     if (!ok && lane == 0) *A.status = 1;
   }
-
-  __syncthreads();
-  if (A.do_x) flush_rows(acc_f, A.xg, xgoff, A.xoff, A.nx, A.x_atomic != 0);
-  if (A.do_y) flush_rows(acc_f, A.yg, ygoff, A.yoff, A.ny, A.y_atomic != 0);
 }
 
 }  // namespace
@@ -652,13 +643,15 @@ int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s, int min_groups) {
   a.ny = (int)c.y.size();
   a.ng = (int)c.r.size();
   a.cell_floats = off;
-  const size_t fixed = ((size_t)kHeaderBytes + (size_t)8 * off + (size_t)kConsumers * J * 256 + 1023) & ~(size_t)1023;
-  auto stages_that_fit = [&](size_t stage_bytes) {
+  auto fixed_bytes = [&](int consumers) {
+    return ((size_t)kHeaderBytes + (size_t)4 * off + (size_t)consumers * J * 256 + 1023) & ~(size_t)1023;
+  };
+  auto stages_that_fit = [&](size_t fixed, size_t stage_bytes) {
     int ns = kMaxStages;
     while (ns >= 2 && fixed + (size_t)ns * stage_bytes > 227 * 1024) ns--;
     return ns;
   };
-  if (stages_that_fit(Stage<false>::kBytes) < 2) return -1;
+  if (stages_that_fit(fixed_bytes(Stage<false>::kConsumers), Stage<false>::kBytes) < 2) return -1;
 
   std::vector<int> key = {10 /*family*/, (int)c.x.size(), (int)c.y.size(), (int)c.r.size()};
   for (const auto& p : c.x) { key.push_back(p.l); key.push_back(p.n); }
@@ -715,11 +708,11 @@ int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s, int min_groups) {
               // xg warps: y rows downwards from m2 = m - lo, accumulator rows upwards from m1 = lo
               p.h_items.push_back(make_int4(head | ((2 * l1 + 1) << 24), kHeaderBytes + 4 * (yoff[yi] + 2 * b0 + 2 * n2 * j2hi),
                                             -8 * n2, 256 * jlo));
-              p.h_items.push_back(make_int4(256, xoff[xi] + 2 * a0, 2 * n1, 0));
+              p.h_items.push_back(make_int4(256, xi, 2 * a0, 0));
               // yg warps: x rows upwards from m1 = lo, accumulator rows downwards from m2 = m - lo
               p.h_items.push_back(make_int4(head | ((2 * l2 + 1) << 24), kHeaderBytes + 4 * (xoff[xi] + 2 * a0 + 2 * n1 * jlo),
                                             8 * n1, 256 * j2hi));
-              p.h_items.push_back(make_int4(-256, yoff[yi] + 2 * b0, 2 * n2, 0));
+              p.h_items.push_back(make_int4(-256, yi, 2 * b0, 0));
               p.h_items.push_back(make_int4(head | (n2 << 16), (int)(quads.size() / 4), sw[0], sw[1]));
               p.h_items.push_back(make_int4(sw[2], sw[3], sw[4], sw[5]));
               p.h_items.push_back(make_int4(sw[6], sw[7], 0, 0));
@@ -738,9 +731,12 @@ int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s, int min_groups) {
                 }
             }
           }
-          if (p.h_items.size() > first_rec) {  // mark the last group of the pair-tile in both descriptors
-            p.h_items[p.h_items.size() - kRec].x |= 0x10000;
-            p.h_items[p.h_items.size() - kRec + 2].x |= 0x10000;
+          // mark the last group of the pair-tile in both descriptors (bit 16), and the last group of either parity
+          // (bit 17: with two sets of consumer warps, each set's last group of the tile)
+          for (size_t b = 1; b <= 2 && p.h_items.size() >= first_rec + b * kRec; b++) {
+            const int bits = b == 1 ? 0x30000 : 0x20000;
+            p.h_items[p.h_items.size() - b * kRec].x |= bits;
+            p.h_items[p.h_items.size() - b * kRec + 2].x |= bits;
           }
         }
     }
@@ -772,18 +768,19 @@ int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s, int min_groups) {
 
   TmaMaps maps;
   memset(&maps, 0, sizeof(maps));
-  const bool tma = pair_tma() && encode_maps(c, plan->h_jobs, a, maps);
+  const size_t fixed_tma = fixed_bytes(Stage<true>::kConsumers), fixed = fixed_bytes(Stage<false>::kConsumers);
+  const bool tma = pair_tma() && stages_that_fit(fixed_tma, Stage<true>::kBytes) >= 3 && encode_maps(c, plan->h_jobs, a, maps);
   cudaError_t e;
   if (tma) {
-    a.nstages = stages_that_fit(Stage<true>::kBytes);
-    const size_t smem = fixed + (size_t)a.nstages * Stage<true>::kBytes;
+    a.nstages = stages_that_fit(fixed_tma, Stage<true>::kBytes);
+    const size_t smem = fixed_tma + (size_t)a.nstages * Stage<true>::kBytes;
     e = cudaFuncSetAttribute(cg_bwd_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess) {
       cg_bwd_pair_kernel<true><<<(unsigned)c.cg.ncells, Stage<true>::kThreads, smem, s>>>(a, maps, J);
       e = cudaGetLastError();
     }
   } else {
-    a.nstages = stages_that_fit(Stage<false>::kBytes);
+    a.nstages = stages_that_fit(fixed, Stage<false>::kBytes);
     const size_t smem = fixed + (size_t)a.nstages * Stage<false>::kBytes;
     e = cudaFuncSetAttribute(cg_bwd_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess) {
