@@ -15,19 +15,26 @@
 // 7651 combinations + 2149 contractions per cell in place of 7651 contractions (0.78 of the multiply-adds, 0.28 of
 // the operand-row reads).
 //
-// Organisation.  One CTA per cell; x and y rows and the gradient accumulators of the cell live in shared memory.
-// Four copy warps (one per scheduler) walk a list of groups -- (pair, 32 x 32 channel tile, row m, up to four output l) -- and bring
-// the slabs g_l[m] of a group (32 rows of 256 bytes each), the group's coefficients and its two consumer descriptors
-// into a four-stage ring with 16-byte asynchronous copies (cp.async, completion counted on an mbarrier; slab rows
-// padded to 272 bytes so both read patterns are conflict-free; one bulk copy per row was tried first and was
-// bound by the copy engine's rate of 256-byte requests).
+// Organisation.  One CTA per cell; the x and y rows of the cell live in shared memory.  A copy warp walks a list of
+// groups -- (pair, 32 x 32 channel tile, row m, up to four output l) -- and brings the slabs g_l[m] of a group
+// (32 rows of 256 bytes each), the group's coefficients and its two consumer descriptors into a four-stage ring:
+// one thread issues two tensor copies per slab (cp.async.bulk.tensor, 128-byte swizzle, so both read patterns
+// below are conflict-free without padding) and two bulk copies, all completing on the stage's mbarrier.  Views that a
+// rank-5 tensor map cannot describe take four copy warps with 16-byte cp.async and rows padded to 272 bytes instead
+// (one bulk copy per row was tried first and was bound by the copy engine's rate of 256-byte requests).
 // Eight consumer warps share every group: warps 0-3 produce xg (lane = n1, each warp one quarter of n2, so the sum
 // over n2 stays inside a lane), warps 4-7 produce yg (lane = n2, each warp one quarter of n1).  A warp copies its
-// quarter of each slab into registers and loops over the band, two entries at a time; the running sums for every m1
-// (resp. m2) of the pair live in a private shared-memory block of the warp (one 8-byte slot per lane and row: plain
-// load / add / store, conflict-free) until the pair-tile ends, then go to the CTA's accumulators with one atomic per
-// value.  No shuffles, no atomics inside the band loop, no CTA-wide barrier between groups.  The four warps of a role add into the same accumulator in no fixed
-// order, so gradients are reproducible to rounding (about 1e-7 relative), not bitwise.
+// quarter of each slab into registers, forms H with packed f32x2 multiply-adds (one instruction per complex number
+// and slab) and loops over the band, two entries at a time; the running sums for every m1 (resp. m2) of the pair live
+// in a private shared-memory block of the warp (one 8-byte slot per lane and row: plain load / add / store,
+// conflict-free) until the pair-tile ends, then go straight to global memory with one vector reduction
+// (red.global.add.v2.f32) per complex number: the cell's rows stay in L2 until the CTA is done, and no CTA-wide
+// accumulator, barrier or flush pass is left.  No shuffles and no atomics inside the band loop.  The four warps of a
+// role, and the pairs that share a row, add in no fixed order, so gradients are reproducible to rounding (about 1e-7
+// relative), not bitwise.
+// Measured and slower: a second set of eight consumer warps on alternate groups (96 registers per thread: 18.4 ms
+// against 15.3), groups of five to seven slabs (three stages instead of four), packed arithmetic for the
+// contraction as well (needs the operands staged twice).
 //
 // Every wait on an mbarrier is bounded; on a timeout the kernel records it in a host-mapped status word, leaves its
 // loops, lets its copies in flight land, and returns; the C ABI reports the failure on the next call.
@@ -97,7 +104,8 @@ struct PairArgs {
   //   {nslab | band length<<8 | last<<16 | accumulator rows of the pair<<24,
   //    byte offset in shared memory of the other operand's row for the first band entry (tile column 0),
   //    its signed step in bytes, byte offset of the first entry's row in a warp's private rows, its step (+-256),
-  //    float offset of the pair-tile's rows in the CTA accumulators, their pitch in floats, 0}
+  //    index of the gradient part the pair-tile adds to, float offset of the tile's first channel in a row, 0}
+  //   last: bit 16 on the last group of the pair-tile, bit 17 on the last group of either parity
   // [4..6] for the producer:
   //   {nslab | band length<<8 | n2<<16, index of the first coefficient quad, 4 x {ri | (m+l)<<8 | map<<16 | colblk<<21,
   //    c1}, 0, 0}: the tile's first channel inside part ri is c1 * n2 + 32 * colblk

@@ -65,7 +65,7 @@ Options& options() {
     const char* inj = getenv("GELIB_B200_INJECT_TIMEOUT");
     o.inject = inj && atoi(inj) != 0;
     const char* tma = getenv("GELIB_B200_PAIR_TMA");
-    o.pair_tma = !(tma && *tma && atoi(tma) == 0);
+    o.pair_tma = !(tma && !strcmp(tma, "0"));
   });
   return o;
 }
@@ -92,7 +92,7 @@ int set_option(const char* name, const char* value) {
     return GELIB_OK;
   }
   if (!strcmp(name, "pair_tma")) {
-    o.pair_tma = !(value && *value && atoi(value) == 0);
+    o.pair_tma = !(value && !strcmp(value, "0"));  // "0": always the cp.async producer; anything else: tensor copies when possible
     return GELIB_OK;
   }
   if (!strcmp(name, "inject_timeout")) {

@@ -338,6 +338,44 @@ def test_vec_backward_named_kernel(G, oracle, opt, B, tau_x, tau_y, maxl, tol, b
         assert rel_err(p - 1, 2 * w) < tol
 
 
+@pytest.mark.parametrize("copies", ["tensor", "cp.async"])
+@pytest.mark.parametrize("layout", ["dense", "sliced"])
+def test_pair_backward_on_grids(G, oracle, opt, copies, layout):
+    """The pair backward kernel on a (batch, g0, g1) grid of cells.  A dense grid merges into one dimension of the
+    kernel's tensor maps; a grid cut out of a larger one has three independent cell dimensions, which a rank-5 map
+    cannot hold, so there the kernel fills its ring with cp.async even when tensor copies are allowed.  Both ways of
+    copying must give the oracle's gradients on the flattened cells."""
+    opt("bwd", "pair!")
+    opt("pair_tma", "1" if copies == "tensor" else "0")
+    B, G0, G1 = 2, 2, 3
+    tau_x, tau_y = {0: 32, 1: 32}, {1: 32, 2: 64}
+    tau_r = oracle.cg_type(tau_x, tau_y, 3, False)
+    pad = 1 if layout == "sliced" else 0
+
+    def grid(seed, l, n):
+        t = crandn(seed, B * G0 * (G1 + pad), 2 * l + 1, n).reshape(B, G0, G1 + pad, 2 * l + 1, n)
+        return dev(t)[:, :, :G1]
+
+    x = {l: grid(500 + l, l, n) for l, n in tau_x.items()}
+    y = {l: grid(520 + l, l, n) for l, n in tau_y.items()}
+    g = {l: grid(540 + l, l, n) for l, n in tau_r.items()}
+    flat = lambda t: np_c(t.reshape(B * G0 * G1, t.shape[-2], t.shape[-1]).cpu())
+    xg_w = {l: np.zeros((B * G0 * G1, 2 * l + 1, n), np.complex64) for l, n in tau_x.items()}
+    yg_w = {l: np.zeros((B * G0 * G1, 2 * l + 1, n), np.complex64) for l, n in tau_y.items()}
+    gn = {l: flat(t) for l, t in g.items()}
+    oracle.vec_cg_back0(xg_w, gn, {l: flat(t) for l, t in y.items()}, False)
+    oracle.vec_cg_back1(yg_w, gn, {l: flat(t) for l, t in x.items()}, False)
+    xg = [torch.zeros(B, G0, G1, 2 * l + 1, n, dtype=torch.complex64, device="cuda") for l, n in tau_x.items()]
+    yg = [torch.zeros(B, G0, G1, 2 * l + 1, n, dtype=torch.complex64, device="cuda") for l, n in tau_y.items()]
+    V = G.backend.SO3vec.view
+    assert G.backend.SO3vec.addCGproduct_back01(V(xg), V(yg), V(list(g.values())), V(list(x.values())), V(list(y.values())))
+    torch.cuda.synchronize()
+    for p, w in zip(xg, xg_w.values()):
+        assert rel_err(p.reshape(w.shape), w) < TOL_BIG
+    for p, w in zip(yg, yg_w.values()):
+        assert rel_err(p.reshape(w.shape), w) < TOL_BIG
+
+
 @pytest.mark.parametrize("B,tau_x,tau_y,maxl,tol", TC_CASES)
 @pytest.mark.parametrize("kernel", ["tcgen05!", "simt", "auto"])
 def test_vec_forward_named_kernel(G, oracle, opt, B, tau_x, tau_y, maxl, tol, kernel):
