@@ -78,7 +78,7 @@ TRAFFIC_RATIO = {
     "cg_fwd_tc_kernel": (0.98, "cfg3, batch 296, ncu 2025.2 --set full"),
     "cg_fwd_kernel": (0.98, "cfg3, batch 296, ncu 2025.2 --set full"),
     "cg_bwd_kernel": (1.002, "cfg3, batch 296, ncu 2025.2 --set full"),
-    "cg_bwd_pair_kernel": (1.0025, "cfg3, batch 296, ncu 2025.2 --set full"),
+    "cg_bwd_pair_kernel": (1.016, "cfg3, batch 296, ncu 2025.2 --set full"),
 }
 
 

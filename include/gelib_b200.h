@@ -221,9 +221,11 @@ double gelib_probe_fp32_tflops(float* scratch, int ctas, int reps, void* stream)
  * (cuda/SO3part_addCGproduct.cu:226-262: tiled or not, coefficients preloaded or not) with no way to steer it;
  * here the choice can be pinned.  name "fwd": "auto" | "simt" | "tcgen05" | "tcgen05!";  name "bwd": "auto" |
  * "simt" | "pair" | "pair!" | "tcgen05" | "tcgen05!" (a trailing "!" refuses calls the named kernel cannot take
- * instead of falling back);  name "inject_timeout": "0" | "1" (tests: one bounded device wait is made to run out).
- * Initial values: the environment variables GELIB_B200_FWD, GELIB_B200_BWD, GELIB_B200_INJECT_TIMEOUT, read once
- * at first use.  Returns GELIB_OK or GELIB_INVALID. */
+ * instead of falling back);  name "pair_tma": "1" | "0" (the pair backward kernel fills its ring with tensor copies
+ * when the views of g fit rank-5 tensor maps, "0": always with cp.async);  name "inject_timeout": "0" | "1" (tests:
+ * one bounded device wait is made to run out).
+ * Initial values: the environment variables GELIB_B200_FWD, GELIB_B200_BWD, GELIB_B200_PAIR_TMA,
+ * GELIB_B200_INJECT_TIMEOUT, read once at first use.  Returns GELIB_OK or GELIB_INVALID. */
 int gelib_set_option(const char* name, const char* value);
 
 /* The kernels that wait on mbarriers bound every wait; one that gives up records it in host-mapped memory and
