@@ -483,6 +483,10 @@ namespace gelib_b200 {
 
 int launch_cg_narrow_bwd(const VecCall& c, cudaStream_t s) {
   static const char* fn = "SO3vec_addCGproduct_back";
+  if (c.xg.empty() && narrow1_enabled()) {  // only the gradient of y is wanted: single-channel x has a kernel of its own
+    const int st = launch_cg_narrow1_bwd(c, s);
+    if (st != -1) return st;
+  }
   NarrowArgs a;
   if (!narrow_setup(c, a)) return -1;
   for (const auto& p : c.y) {

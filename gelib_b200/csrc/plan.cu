@@ -37,7 +37,7 @@ bool upload(const std::vector<T>& h, T** d) {
 
 namespace {
 struct Options {
-  std::atomic<int> fwd{kFwdAuto}, bwd{kBwdAuto}, inject{0}, pair_tma{1};
+  std::atomic<int> fwd{kFwdAuto}, bwd{kBwdAuto}, inject{0}, pair_tma{1}, narrow1{1};
 };
 int parse_fwd(const char* v) {
   if (!v || !*v || !strcmp(v, "auto")) return kFwdAuto;
@@ -75,6 +75,7 @@ int fwd_mode() { return options().fwd.load(std::memory_order_relaxed); }
 int bwd_mode() { return options().bwd.load(std::memory_order_relaxed); }
 bool inject_timeout() { return options().inject.load(std::memory_order_relaxed) != 0; }
 bool pair_tma() { return options().pair_tma.load(std::memory_order_relaxed) != 0; }
+bool narrow1_enabled() { return options().narrow1.load(std::memory_order_relaxed) != 0; }
 
 int set_option(const char* name, const char* value) {
   if (!name) return GELIB_INVALID;
@@ -89,6 +90,10 @@ int set_option(const char* name, const char* value) {
     const int v = parse_bwd(value);
     if (v < 0) return GELIB_INVALID;
     o.bwd = v;
+    return GELIB_OK;
+  }
+  if (!strcmp(name, "narrow1")) {
+    o.narrow1 = !(value && !strcmp(value, "0"));
     return GELIB_OK;
   }
   if (!strcmp(name, "pair_tma")) {

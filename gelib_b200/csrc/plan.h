@@ -38,6 +38,8 @@ int launch_cg_bwd(const VecCall& c, cudaStream_t s);
 int launch_cg_bwd_tc(const VecCall& c, cudaStream_t s);  // tcgen05 kernel; -1 when the call does not qualify
 int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s, int min_groups);  // uncoupled-gradient kernel; -1 when the call does not qualify or has fewer groups per cell
 int launch_cg_narrow_bwd(const VecCall& c, cudaStream_t s);
+int launch_cg_narrow1_bwd(const VecCall& c, cudaStream_t s);  // x with one channel, gradient of y only; -1 otherwise
+bool narrow1_enabled();  // option "narrow1" (default on): tests compare the two kernels
 int launch_cg_narrow_fwd(const VecCall& c, cudaStream_t s);  // x with at most 4 channels; -1 when the call does not qualify
 int launch_cg_strided(const VecCall& c, int mode, cudaStream_t s);  // mode 0 fwd, 1 back0, 2 back1
 int launch_cg_strided_static(const VecCall& c, cudaStream_t s);  // forward, tables in a static device array: no allocation

@@ -34,7 +34,7 @@ def opt(G):
 
     yield set_
     for name in touched:
-        G._lib.set_option(name, "0" if name == "inject_timeout" else "auto")
+        G._lib.set_option(name, "0" if name == "inject_timeout" else "auto")  # "auto" = on for pair_tma, narrow1
 
 
 def dev(t):
@@ -336,6 +336,34 @@ def test_vec_backward_named_kernel(G, oracle, opt, B, tau_x, tau_y, maxl, tol, b
         assert rel_err(p - 1, 2 * w) < tol
     for p, w in zip(yg, yg_w.values()):
         assert rel_err(p - 1, 2 * w) < tol
+
+
+@pytest.mark.parametrize("kernel", ["single-channel", "general"])
+@pytest.mark.parametrize("B,lx,tau_y,maxl,bcast", [
+    (5, 3, {0: 16, 1: 16, 2: 16, 3: 16}, 3, False),     # two cells per warp
+    (3, 2, {1: 5, 2: 5}, 4, False),                      # channel count that is not a power of two, gaps in l
+    (4, 4, {0: 32, 2: 32}, 6, False),                    # one cell per warp, truncated output
+    (6, 2, {0: 8, 1: 8, 2: 8}, 2, True),                 # y broadcast over the batch: its gradient is a sum over cells
+])
+def test_gradient_of_y_for_single_channel_x(G, oracle, opt, B, lx, tau_y, maxl, bcast, kernel):
+    """back1 alone with a one-channel x (the first layer after spherical harmonics): the kernel that walks the band
+    once per (l1,l2) pair and the general narrow kernel must both give the oracle's gradient, on top of what yg holds."""
+    opt("narrow1", "1" if kernel == "single-channel" else "0")
+    tau_x = {l: 1 for l in range(lx + 1)}
+    x, y = _vec_inputs(tau_x, tau_y, B, 700)
+    if bcast:
+        y = {l: t[:1].contiguous() for l, t in y.items()}
+    tau_r = oracle.cg_type(tau_x, tau_y, maxl, False)
+    g = {l: crandn(730 + l, B, 2 * l + 1, n) for l, n in tau_r.items()}
+    yg_w = {l: np.zeros(t.shape, np.complex64) for l, t in y.items()}
+    oracle.vec_cg_back1(yg_w, {l: np_c(t) for l, t in g.items()}, {l: np_c(t) for l, t in x.items()}, False)
+    V = G.backend.SO3vec.view
+    yg = [torch.ones(t.shape, dtype=torch.complex64, device="cuda") for t in y.values()]
+    for _ in range(2):
+        assert V(yg).addCGproduct_back1(V([dev(t) for t in g.values()]), V([dev(t) for t in x.values()]))
+    torch.cuda.synchronize()
+    for p, w in zip(yg, yg_w.values()):
+        assert rel_err(p - 1, 2 * w) < TOL_BIG
 
 
 @pytest.mark.parametrize("copies", ["tensor", "cp.async"])
