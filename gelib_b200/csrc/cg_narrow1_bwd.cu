@@ -93,28 +93,52 @@ __device__ __forceinline__ void fetch_group(const Narrow1Args& A, int gi, const 
   }
 }
 
-// The band of one group: H from the registers, H conj(x[m1]) into the lane's slots of the warp's block.  The
-// coefficients of entry k+1 are requested before entry k is worked on.
+// One band entry: H from the registers, H conj(x[m1]) into the lane's slot of row m2.
+template <int NL>
+__device__ __forceinline__ void band_entry(const float4 c, const GroupRegs& G, const float2 xv, float2* slot) {
+  f32x2 h = mul2(pack2(c.x, c.x), G.g[0]);
+  if (NL > 1) h = fma2(pack2(c.y, c.y), G.g[1], h);
+  if (NL > 2) h = fma2(pack2(c.z, c.z), G.g[2], h);
+  if (NL > 3) h = fma2(pack2(c.w, c.w), G.g[3], h);
+  float hr, hi;
+  unpack2(h, hr, hi);
+  float2 a = *slot;
+  a.x = fmaf(hr, xv.x, a.x); a.x = fmaf(hi, xv.y, a.x);
+  a.y = fmaf(hi, xv.x, a.y); a.y = fmaf(-hr, xv.y, a.y);
+  *slot = a;
+}
+
+// The band of one group, two entries per turn: the coefficients of an entry are requested while the entry before
+// it is worked on (two register sets, used alternately).  Rows m2 = m - m1 descend as m1 ascends.
+template <int NL>
+__device__ __forceinline__ void run_band(const float4* __restrict__ cf, int cnt, const GroupRegs& G, const float2* xp, float2* ya) {
+  float4 c0 = __ldg(cf), c1;
+  int k = 0;
+  for (; k + 2 < cnt; k += 2) {
+    c1 = __ldg(cf + k + 1);
+    band_entry<NL>(c0, G, xp[k], ya - 32 * k);
+    c0 = __ldg(cf + k + 2);
+    band_entry<NL>(c1, G, xp[k + 1], ya - 32 * (k + 1));
+  }
+  if (k + 1 < cnt) {
+    c1 = __ldg(cf + k + 1);
+    band_entry<NL>(c0, G, xp[k], ya - 32 * k);
+    band_entry<NL>(c1, G, xp[k + 1], ya - 32 * (k + 1));
+  } else {
+    band_entry<NL>(c0, G, xp[k], ya - 32 * k);
+  }
+}
+
 __device__ __forceinline__ void run_group(const float4* __restrict__ coef, const GroupRegs& G, const float2* xs, float2* yacc) {
   const int cnt = (G.h.x >> 8) & 255;
   const float4* cf = coef + G.h.w;
   const float2* xp = xs + G.h.y;
   float2* ya = yacc + 32 * G.h.z;
-  float4 c = __ldg(cf);
-  for (int k = 0; k < cnt; k++) {
-    const float4 cn = __ldg(cf + (k + 1 < cnt ? k + 1 : k));
-    f32x2 h = mul2(pack2(c.x, c.x), G.g[0]);
-    h = fma2(pack2(c.y, c.y), G.g[1], h);
-    h = fma2(pack2(c.z, c.z), G.g[2], h);
-    h = fma2(pack2(c.w, c.w), G.g[3], h);
-    float hr, hi;
-    unpack2(h, hr, hi);
-    const float2 xv = xp[k];
-    float2 a = ya[-32 * k];  // row m2 = m - m1, descending
-    a.x = fmaf(hr, xv.x, a.x); a.x = fmaf(hi, xv.y, a.x);
-    a.y = fmaf(hi, xv.x, a.y); a.y = fmaf(-hr, xv.y, a.y);
-    ya[-32 * k] = a;
-    c = cn;
+  switch (G.h.x & 255) {
+    case 1: run_band<1>(cf, cnt, G, xp, ya); break;
+    case 2: run_band<2>(cf, cnt, G, xp, ya); break;
+    case 3: run_band<3>(cf, cnt, G, xp, ya); break;
+    default: run_band<4>(cf, cnt, G, xp, ya); break;
   }
 }
 
