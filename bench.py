@@ -87,7 +87,7 @@ def kernel_name(args, dom):
     if args.workload == "cfg4":
         return "diag_fwd_cell_kernel" if dom == "forward" else "diag_bwd_cell_kernel"
     if args.workload == "cfg5":
-        return "cg_narrow_fwd_kernel" if dom == "forward" else "cg_narrow_bwd_kernel"
+        return "cg_narrow_fwd_kernel" if dom == "forward" else "cg_narrow1_bwd_kernel"
     if dom == "forward":
         tc = args.fwd_kernel == "tcgen05" or (args.fwd_kernel == "auto" and args.workload == "cfg3")
         return "cg_fwd_tc_kernel" if tc else "cg_fwd_kernel"

@@ -75,12 +75,15 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
 struct GroupRegs {
   int4 h;
   f32x2 g[kGroupL];
+  float4 cq;  // lane k: the coefficient quad of band entry k
 };
 
 __device__ __forceinline__ void fetch_group(const Narrow1Args& A, int gi, const long long* gbase, int goff, bool ok, GroupRegs& R) {
   const int4* rec = A.recs + kRec * gi;
   R.h = __ldg(rec);
   const int nl = R.h.x & 255;
+  const int lane = threadIdx.x & 31;
+  R.cq = __ldg(A.coef + R.h.w + min(lane, ((R.h.x >> 8) & 255) - 1));
 #pragma unroll
   for (int q = 0; q < kGroupL / 2; q++) {
     R.g[2 * q] = R.g[2 * q + 1] = 0ull;
@@ -111,17 +114,17 @@ __device__ __forceinline__ void band_entry(const float4 c, const GroupRegs& G, c
 // The band of one group, two entries per turn: the coefficients of an entry are requested while the entry before
 // it is worked on (two register sets, used alternately).  Rows m2 = m - m1 descend as m1 ascends.
 template <int NL>
-__device__ __forceinline__ void run_band(const float4* __restrict__ cf, int cnt, const GroupRegs& G, const float2* xp, float2* ya) {
-  float4 c0 = __ldg(cf), c1;
+__device__ __forceinline__ void run_band(const float4* cf, int cnt, const GroupRegs& G, const float2* xp, float2* ya) {
+  float4 c0 = cf[0], c1;
   int k = 0;
   for (; k + 2 < cnt; k += 2) {
-    c1 = __ldg(cf + k + 1);
+    c1 = cf[k + 1];
     band_entry<NL>(c0, G, xp[k], ya - 32 * k);
-    c0 = __ldg(cf + k + 2);
+    c0 = cf[k + 2];
     band_entry<NL>(c1, G, xp[k + 1], ya - 32 * (k + 1));
   }
   if (k + 1 < cnt) {
-    c1 = __ldg(cf + k + 1);
+    c1 = cf[k + 1];
     band_entry<NL>(c0, G, xp[k], ya - 32 * k);
     band_entry<NL>(c1, G, xp[k + 1], ya - 32 * (k + 1));
   } else {
@@ -129,9 +132,11 @@ __device__ __forceinline__ void run_band(const float4* __restrict__ cf, int cnt,
   }
 }
 
-__device__ __forceinline__ void run_group(const float4* __restrict__ coef, const GroupRegs& G, const float2* xs, float2* yacc) {
+__device__ __forceinline__ void run_group(float4* cf, const GroupRegs& G, const float2* xs, float2* yacc) {
   const int cnt = (G.h.x >> 8) & 255;
-  const float4* cf = coef + G.h.w;
+  __syncwarp();                       // the band of the group before has been read
+  cf[threadIdx.x & 31] = G.cq;        // the group's coefficients: one quad per lane, read back by every lane
+  __syncwarp();
   const float2* xp = xs + G.h.y;
   float2* ya = yacc + 32 * G.h.z;
   switch (G.h.x & 255) {
@@ -142,6 +147,7 @@ __device__ __forceinline__ void run_group(const float4* __restrict__ coef, const
   }
 }
 
+template <bool kSph>  // x generated from the cell's point (fused first layer) instead of read
 __global__ void __launch_bounds__(256, 4) cg_narrow1_bwd_kernel(const __grid_constant__ Narrow1Args A) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -153,12 +159,13 @@ __global__ void __launch_bounds__(256, 4) cg_narrow1_bwd_kernel(const __grid_con
   // per warp: [g part bases: WC x kMaxParts pointers][x rows of the WC cells][yacc: the rows of one l2 x 32 lanes]
   unsigned char* wb = smem_raw + (size_t)warp * A.warp_bytes;
   long long* gbase = reinterpret_cast<long long*>(wb) + lc * kMaxParts;
-  float2* xs = reinterpret_cast<float2*>(wb + 8 * WC * kMaxParts) + lc * A.xrows;
-  float2* yacc = reinterpret_cast<float2*>(wb + 8 * WC * kMaxParts + 8 * WC * A.xrows) + lane;
+  float2* xs = reinterpret_cast<float2*>(wb + 512 + 8 * WC * kMaxParts) + lc * A.xrows;
+  float4* cbuf = reinterpret_cast<float4*>(wb + 8 * WC * kMaxParts);  // 32 coefficient quads of the group at work
+  float2* yacc = reinterpret_cast<float2*>(wb + 512 + 8 * WC * kMaxParts + 8 * WC * A.xrows) + lane;
 
   for (int p = n2l; p < A.ng; p += CW)
     gbase[p] = reinterpret_cast<long long>(A.g[p].base + (cell_ok ? cell_offset(A.g[p], A.cg, cell) : 0));
-  if (A.sph) {
+  if (kSph) {
     if (n2l == 0) {
       const float* pt = A.sph + (cell_ok ? cell * A.sph_sb : 0);
       spharm_point(cell_ok ? pt[0] : 0.f, cell_ok ? pt[A.sph_sm] : 0.f, cell_ok ? pt[2 * A.sph_sm] : 1.f, A.sph_lmax,
@@ -203,11 +210,11 @@ __global__ void __launch_bounds__(256, 4) cg_narrow1_bwd_kernel(const __grid_con
   if (A.ngroups > 0) fetch_group(A, 0, gbase, goff, ok, ga);
   for (int gi = 0; gi < A.ngroups; gi += 2) {
     if (gi + 1 < A.ngroups) fetch_group(A, gi + 1, gbase, goff, ok, gb);
-    run_group(A.coef, ga, xs, yacc);
+    run_group(cbuf, ga, xs, yacc);
     if (ga.h.x & 0x10000) flush((ga.h.x >> 20) & 0xff);
     if (gi + 1 < A.ngroups) {
       if (gi + 2 < A.ngroups) fetch_group(A, gi + 2, gbase, goff, ok, ga);
-      run_group(A.coef, gb, xs, yacc);
+      run_group(cbuf, gb, xs, yacc);
       if (gb.h.x & 0x10000) flush((gb.h.x >> 20) & 0xff);
     }
   }
@@ -224,6 +231,9 @@ int launch_cg_narrow1_bwd(const VecCall& c, cudaStream_t s) {
   if (n2 < 1 || n2 > 32) return -1;
   for (const auto& p : c.x) if (p.n != 1 || p.l > 100) return -1;
   for (const auto& p : c.y) if (p.n != n2 || p.l > 100) return -1;
+  for (const auto& p : c.x)
+    for (const auto& q : c.y)
+      if (2 * std::min(p.l, q.l) + 1 > 32) return -1;  // a band is at most 32 entries: one coefficient quad per lane
   for (const auto& p : c.r) if (p.l > 200 || p.sm != 2LL * p.n) return -1;  // the records bake the row pitch in
   for (const auto& p : c.r) {
     if (reinterpret_cast<uintptr_t>(p.base) % 8 || (2LL * p.n) % 2) return -1;
@@ -258,7 +268,7 @@ int launch_cg_narrow1_bwd(const VecCall& c, cudaStream_t s) {
   a.sph_sb = c.sph_sb;
   a.sph_sm = c.sph_sm;
   a.sph_lmax = c.sph_lmax;
-  size_t wbytes = (size_t)8 * a.WC * kMaxParts + (size_t)8 * a.WC * a.xrows + (size_t)256 * a.yrows_max;
+  size_t wbytes = (size_t)8 * a.WC * kMaxParts + 512 + (size_t)8 * a.WC * a.xrows + (size_t)256 * a.yrows_max;
   wbytes = (wbytes + 15) / 16 * 16;
   a.warp_bytes = (int)wbytes;
   const int nwarps = 8;
@@ -320,8 +330,14 @@ int launch_cg_narrow1_bwd(const VecCall& c, cudaStream_t s) {
   a.offs_extra = c.offs_extra;
   const long long blocks = (c.cg.ncells + (long long)a.WC * nwarps - 1) / ((long long)a.WC * nwarps);
   if (blocks > 0x7fffffffLL) return -1;
-  cudaError_t e = cudaFuncSetAttribute(cg_narrow1_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e == cudaSuccess) cg_narrow1_bwd_kernel<<<(unsigned)blocks, nwarps * 32, smem, s>>>(a);
+  cudaError_t e;
+  if (a.sph) {
+    e = cudaFuncSetAttribute(cg_narrow1_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) cg_narrow1_bwd_kernel<true><<<(unsigned)blocks, nwarps * 32, smem, s>>>(a);
+  } else {
+    e = cudaFuncSetAttribute(cg_narrow1_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) cg_narrow1_bwd_kernel<false><<<(unsigned)blocks, nwarps * 32, smem, s>>>(a);
+  }
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return check_cuda(e, fn, "single-channel backward kernel launch");
   count_launch();
