@@ -222,7 +222,9 @@ double gelib_probe_fp32_tflops(float* scratch, int ctas, int reps, void* stream)
  * here the choice can be pinned.  name "fwd": "auto" | "simt" | "tcgen05" | "tcgen05!";  name "bwd": "auto" |
  * "simt" | "pair" | "pair!" | "tcgen05" | "tcgen05!" (a trailing "!" refuses calls the named kernel cannot take
  * instead of falling back);  name "pair_tma": "1" | "0" (the pair backward kernel fills its ring with tensor copies
- * when the views of g fit rank-5 tensor maps, "0": always with cp.async);  name "inject_timeout": "0" | "1" (tests:
+ * when the views of g fit rank-5 tensor maps, "0": always with cp.async);  name "narrow1": "1" | "0" (the
+ * gradient of y for a one-channel x takes the kernel written for that shape, "0": the general narrow kernel);
+ * name "inject_timeout": "0" | "1" (tests:
  * one bounded device wait is made to run out).
  * Initial values: the environment variables GELIB_B200_FWD, GELIB_B200_BWD, GELIB_B200_PAIR_TMA,
  * GELIB_B200_INJECT_TIMEOUT, read once at first use.  Returns GELIB_OK or GELIB_INVALID. */
