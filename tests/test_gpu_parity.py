@@ -338,6 +338,32 @@ def test_vec_backward_named_kernel(G, oracle, opt, B, tau_x, tau_y, maxl, tol, b
         assert rel_err(p - 1, 2 * w) < tol
 
 
+@pytest.mark.parametrize("overwrite", [True, False])
+@pytest.mark.parametrize("B,lx,tau_y,maxl,bcast", [
+    (5, 3, {0: 16, 1: 16, 2: 16, 3: 16}, 3, False),     # two cells per warp
+    (3, 2, {1: 5, 2: 5}, 4, False),                      # channel count that is not a power of two, gaps in l
+    (4, 4, {0: 32, 2: 32}, 6, False),                    # one cell per warp, truncated output
+    (6, 2, {0: 8, 1: 8, 2: 8}, 2, True),                 # y broadcast over the batch
+])
+def test_forward_for_single_channel_x(G, oracle, B, lx, tau_y, maxl, bcast, overwrite):
+    """The forward with a one-channel x (the narrow kernel) against the oracle, overwriting an output full of garbage
+    and accumulating on top of ones."""
+    tau_x = {l: 1 for l in range(lx + 1)}
+    x, y = _vec_inputs(tau_x, tau_y, B, 800)
+    if bcast:
+        y = {l: t[:1].contiguous() for l, t in y.items()}
+    tau_r = oracle.cg_type(tau_x, tau_y, maxl, False)
+    want = {l: np.zeros((B, 2 * l + 1, n), np.complex64) for l, n in tau_r.items()}
+    oracle.vec_cg(want, {l: np_c(t) for l, t in x.items()}, {l: np_c(t) for l, t in y.items()}, False)
+    V = G.backend.SO3vec.view
+    fill = 7.0 + 3.0j if overwrite else 1.0
+    rs = [torch.full((B, 2 * l + 1, n), fill, dtype=torch.complex64, device="cuda") for l, n in tau_r.items()]
+    assert V(rs).addCGproduct(V([dev(t) for t in x.values()]), V([dev(t) for t in y.values()]), overwrite=overwrite)
+    torch.cuda.synchronize()
+    for p, w in zip(rs, want.values()):
+        assert rel_err(p if overwrite else p - 1, w) < TOL
+
+
 @pytest.mark.parametrize("kernel", ["single-channel", "general"])
 @pytest.mark.parametrize("B,lx,tau_y,maxl,bcast", [
     (5, 3, {0: 16, 1: 16, 2: 16, 3: 16}, 3, False),     # two cells per warp
