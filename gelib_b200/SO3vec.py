@@ -55,6 +55,29 @@ def _vec_backward(ctx, gargs):
     return tuple([None, None, None] + grads)
 
 
+class _MixFn(torch.autograd.Function):
+    """part @ W through gelib_SO3part_mix; gradients g @ W^H and part^H @ g (summed over all rows)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return gb.mix(x, w)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w = ctx.saved_tensors
+        gx = gb.mix(g, w, adjoint=True) if ctx.needs_input_grad[0] else None
+        gw = gb.mix_back_w(x, g, w.size(0), w.size(1)) if ctx.needs_input_grad[1] else None
+        return gx, gw
+
+
+def _mix(p, m):
+    t = p.as_subclass(torch.Tensor) if type(p) is not torch.Tensor else p
+    if gb.mix_supported(t, m):
+        return _MixFn.apply(t, m)
+    return torch.matmul(p, m)
+
+
 class SO3vec_CGproductFn(torch.autograd.Function):
     """python/src/gelib/SO3vec.py:233-270."""
 
@@ -194,8 +217,9 @@ class _VecBase:
         return type(self)(*[self.parts[l] + y.parts[l] for l in self.parts])
 
     def __mul__(self, w):
-        """Channel mixing with SO3weights: part l times the l-th weight matrix (python/src/gelib/SO3vec.py:174-177)."""
-        return type(self)(*[torch.matmul(p, m) for p, m in zip(self.parts.values(), w.parts)])
+        """Channel mixing with SO3weights: part l times the l-th weight matrix (python/src/gelib/SO3vec.py:174-177).
+        On a CUDA device with at most 64 channels the memory-bound mixing kernels do it, otherwise torch.matmul."""
+        return type(self)(*[_mix(p, m) for p, m in zip(self.parts.values(), w.parts)])
 
     def to(self, device):
         return type(self)(*[p.to(device) for p in self.parts.values()])

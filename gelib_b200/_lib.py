@@ -69,6 +69,10 @@ SYMBOLS = {
                                                               ctypes.c_int, ctypes.c_void_p]),
     "gelib_add_gather": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
                                         ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+    "gelib_SO3part_mix": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int,
+                                         ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
+    "gelib_SO3part_mix_back_w": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong,
+                                                ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
     "gelib_SO3irrep_matrix": (ctypes.c_int, [ctypes.c_int, ctypes.c_double, ctypes.c_double, ctypes.c_double, ctypes.c_void_p]),
     "gelib_SO3part_apply": (ctypes.c_int, [_P5, _P5, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]),
     "gelib_kernel_launch_count": (ctypes.c_longlong, []),

@@ -184,6 +184,40 @@ def _gather(r, x, gmap, d, transposed):
                                             col.data_ptr(), stream_of(r)))
 
 
+MIX_MAX_CHANNELS = 64
+
+
+def mix_supported(x, w):
+    """True when (x, w) can take the mixing kernels: CUDA complex64, w a matrix with at most 64 channels a side."""
+    return (x.is_cuda and w.is_cuda and x.dtype == torch.complex64 and w.dtype == torch.complex64 and w.dim() == 2
+            and x.dim() >= 2 and x.size(-1) == w.size(0) and 1 <= w.size(0) <= MIX_MAX_CHANNELS
+            and 1 <= w.size(1) <= MIX_MAX_CHANNELS and x.numel() > 0)
+
+
+def mix(x, w, adjoint=False):
+    """x (.., n_in) times w (n_in, n_out), or with adjoint=True x (.., n_out) times w^H: a new dense tensor."""
+    _one_device(x, w)
+    x, w = x.contiguous(), w.contiguous()
+    n_in, n_out = w.size(0), w.size(1)
+    rows = x.numel() // x.size(-1)
+    r = torch.empty(list(x.shape[:-1]) + [n_in if adjoint else n_out], dtype=torch.complex64, device=x.device)
+    with device_guard(x):
+        check(lib().gelib_SO3part_mix(r.data_ptr(), x.data_ptr(), w.data_ptr(), rows, n_in, n_out, 1 if adjoint else 0,
+                                      stream_of(x)))
+    return r
+
+
+def mix_back_w(x, g, n_in, n_out):
+    """x^H g summed over all rows: the gradient of the weight matrix, (n_in, n_out)."""
+    _one_device(x, g)
+    x, g = x.contiguous(), g.contiguous()
+    rows = x.numel() // x.size(-1)
+    wg = torch.zeros(n_in, n_out, dtype=torch.complex64, device=x.device)
+    with device_guard(x):
+        check(lib().gelib_SO3part_mix_back_w(wg.data_ptr(), x.data_ptr(), g.data_ptr(), rows, n_in, n_out, stream_of(x)))
+    return wg
+
+
 def SO3irrep_matrix(l, alpha, beta, gamma):
     """D^l(alpha, beta, gamma) as a (2l+1, 2l+1) complex64 CPU tensor (SO3irrep::matrix, SO3/SO3irrep.hpp:69-103)."""
     out = torch.zeros(2 * l + 1, 2 * l + 1, dtype=torch.complex64)

@@ -490,6 +490,24 @@ int gelib_add_gather(float* r, const float* x, long long outer, int n_out, int n
   return launch_gather(r, x, outer, n_out, n_in, inner, row_ptr, col, (cudaStream_t)stream);
 }
 
+int gelib_SO3part_mix(float* r, const float* x, const float* W, long long rows, int n_in, int n_out, int mode, void* stream) {
+  static const char* fn = "SO3part_mix";
+  if (rows < 0 || n_in < 0 || n_out < 0 || (mode != 0 && mode != 1)) return fail(GELIB_INVALID, fn, "negative size or unknown mode");
+  if (rows && (!r || !x || !W)) return fail(GELIB_INVALID, fn, "null pointer");
+  if ((reinterpret_cast<uintptr_t>(r) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(W)) % 8)
+    return fail(GELIB_INVALID, fn, "complex arrays must be 8-byte aligned");
+  return launch_mix(r, x, W, rows, n_in, n_out, mode, (cudaStream_t)stream);
+}
+
+int gelib_SO3part_mix_back_w(float* Wg, const float* x, const float* g, long long rows, int n_in, int n_out, void* stream) {
+  static const char* fn = "SO3part_mix_back_w";
+  if (rows < 0 || n_in < 0 || n_out < 0) return fail(GELIB_INVALID, fn, "negative size");
+  if (rows && (!Wg || !x || !g)) return fail(GELIB_INVALID, fn, "null pointer");
+  if ((reinterpret_cast<uintptr_t>(Wg) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(g)) % 8)
+    return fail(GELIB_INVALID, fn, "complex arrays must be 8-byte aligned");
+  return launch_mix_back_w(Wg, x, g, rows, n_in, n_out, (cudaStream_t)stream);
+}
+
 int gelib_SO3irrep_matrix(int l, double alpha, double beta, double gamma, float* out) {
   if (l < 0 || !out) return fail(GELIB_INVALID, "SO3irrep_matrix", "negative l or null output");
   wigner_D(l, alpha, beta, gamma, out);

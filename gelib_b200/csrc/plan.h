@@ -52,6 +52,8 @@ void build_diag_items(DevicePlan& p, const std::vector<PartSig>& xs, const std::
                       const std::vector<PartSig>& rs, int* max_nl);
 int launch_gather(float* r, const float* x, long long outer, int n_out, int n_in, long long inner, const int* row_ptr,
                   const int* col, cudaStream_t s);
+int launch_mix(float* r, const float* x, const float* W, long long rows, int n_in, int n_out, int mode, cudaStream_t s);
+int launch_mix_back_w(float* Wg, const float* x, const float* g, long long rows, int n_in, int n_out, cudaStream_t s);
 int launch_apply(const PartView& r, const PartView& x, const CellGrid& cg, const float* D, int flags, cudaStream_t s);
 void wigner_D(int l, double alpha, double beta, double gamma, float* out);
 int launch_spharm(const std::vector<PartView>& r, const PartView& x, const CellGrid& cg, int flags, cudaStream_t s);

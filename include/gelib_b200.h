@@ -197,6 +197,15 @@ int gelib_SO3vec_addCGproduct_spharm_back1(int ny, const gelib_tensor5* yg, int 
 int gelib_add_gather(float* r, const float* x, long long outer, int n_out, int n_in, long long inner, const int* row_ptr,
                      const int* col, void* stream);
 
+/* Channel mixing of a part by a complex weight matrix (all arrays dense complex64, rows = every (cell, m) of the part):
+ *   mode 0:  r[row][j] = sum_i x[row][i] W[i][j]            r (rows, n_out), x (rows, n_in), W (n_in, n_out)
+ *   mode 1:  r[row][i] = sum_j x[row][j] conj(W[i][j])      r (rows, n_in),  x (rows, n_out): the gradient of the part
+ * and the gradient of the weights,  Wg[i][j] += sum_row conj(x[row][i]) g[row][j].  At most 64 channels on either side
+ * (GELIB_SKIPPED beyond).  In GElib this is torch.matmul per part (python/src/gelib/SO3vec.py:174-177,
+ * python/src/gelib/SO3weights.py:22-85): there is no C++ counterpart. */
+int gelib_SO3part_mix(float* r, const float* x, const float* W, long long rows, int n_in, int n_out, int mode, void* stream);
+int gelib_SO3part_mix_back_w(float* Wg, const float* x, const float* g, long long rows, int n_in, int n_out, void* stream);
+
 /* Wigner matrix D^l of the rotation with z-y-z Euler angles (alpha, beta, gamma), as SO3irrep::matrix builds it
  * (SO3/SO3irrep.hpp:69-103): out[(m1+l)*(2l+1) + (m2+l)] = d^l_{m2 m1}(beta) e^{i m1 alpha} e^{i m2 gamma}, interleaved
  * (re, im) floats, host memory. */

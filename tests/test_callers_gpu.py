@@ -199,3 +199,42 @@ def test_fp64_option_keeps_double_coefficients_and_sums(G):
     e64, e32 = run(True), run(False)
     assert max(e64) < 1.5e-7, e64            # float rounding of the stored result only
     assert max(e32) < 1e-5 and e64[1] < e32[1] and e64[2] < e32[2], (e64, e32)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows_shape,n_in,n_out", [((1000, 5), 16, 16), ((7, 3), 5, 9), ((300, 2, 13), 32, 64), ((1,), 1, 1)])
+def test_weight_mixing_kernels_match_matmul(G, rows_shape, n_in, n_out):
+    """part * W and both of its gradients through the mixing kernels against torch.matmul and its autograd."""
+    torch.manual_seed(11)
+    x = torch.randn(*rows_shape, n_in, dtype=torch.complex64, device="cuda")
+    w = torch.randn(n_in, n_out, dtype=torch.complex64, device="cuda") / n_in ** 0.5
+    g = torch.randn(*rows_shape, n_out, dtype=torch.complex64, device="cuda")
+    want = torch.matmul(x, w)
+    got = G.backend.mix(x, w)
+    assert (got - want).abs().max() < 1e-5 * max(1.0, float(want.abs().max()))
+    gx_w = torch.matmul(g, w.conj().T)
+    gx = G.backend.mix(g, w, adjoint=True)
+    assert (gx - gx_w).abs().max() < 1e-5 * max(1.0, float(gx_w.abs().max()))
+    gw_w = torch.matmul(x.reshape(-1, n_in).conj().T, g.reshape(-1, n_out))
+    gw = G.backend.mix_back_w(x, g, n_in, n_out)
+    assert (gw - gw_w).abs().max() < 2e-5 * max(1.0, float(gw_w.abs().max()))
+
+
+@pytest.mark.gpu
+def test_vec_times_weights_autograd(G):
+    """SO3vec * SO3weights on the device: values and gradients equal those of torch.matmul per part."""
+    torch.manual_seed(12)
+    tau = {0: 16, 1: 16, 2: 16}
+    v = G.SO3vec.randn(9, tau, device="cuda")
+    ws = [torch.randn(16, 8, dtype=torch.complex64, device="cuda").requires_grad_() for _ in tau]
+    ps = [p.detach().clone().requires_grad_() for p in v.parts.values()]
+    out = G.SO3vec(*[G.SO3part(p) for p in ps]) * G.SO3weights(*ws)
+    gs = [torch.randn_like(p) for p in out.parts.values()]
+    torch.autograd.backward(list(out.parts.values()), grad_tensors=gs)
+    for p, w_, g_, o in zip(ps, ws, gs, out.parts.values()):
+        p2, w2 = p.detach().clone().requires_grad_(), w_.detach().clone().requires_grad_()
+        ref = torch.matmul(p2.as_subclass(torch.Tensor), w2)
+        ref.backward(g_.as_subclass(torch.Tensor))
+        assert (o.as_subclass(torch.Tensor) - ref).abs().max() < 1e-5
+        assert (p.grad - p2.grad).abs().max() < 1e-5
+        assert (w_.grad - w2.grad).abs().max() < 1e-4
