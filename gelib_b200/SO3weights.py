@@ -1,7 +1,8 @@
 """``gelib.SO3weights`` / ``SO3linear``: per-l complex mixing matrices (python/src/gelib/SO3weights.py:22-85).
 
-Plain torch on purpose: in the reference the mixing is ``torch.matmul`` per part
-(python/src/gelib/SO3vec.py:174-177), not GElib code.
+In the reference the mixing is ``torch.matmul`` per part (python/src/gelib/SO3vec.py:174-177), not GElib code; here
+``SO3vec.__mul__`` takes the library's mixing kernels on a CUDA device (at most 64 channels a side) and ``torch.matmul``
+otherwise.
 """
 import torch
 
