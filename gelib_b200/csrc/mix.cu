@@ -58,6 +58,45 @@ __global__ void __launch_bounds__(256) mix_kernel(float2* __restrict__ r, const 
   }
 }
 
+// The same product for power-of-two channel counts up to 32 on both sides: the thread keeps its column of the matrix
+// in registers and walks the rows of the tile with 16-byte loads of x (two complex numbers per load).
+template <int MODE, int NK>
+__global__ void __launch_bounds__(256) mix_reg_kernel(float2* __restrict__ r, const float2* __restrict__ x,
+                                                      const float2* __restrict__ W, long long rows, int nj, int w_cols) {
+  extern __shared__ float2 sm[];
+  float2* xs = sm;  // [kTileRows][NK]
+  const int j = threadIdx.x % nj, rg = threadIdx.x / nj, nrg = blockDim.x / nj;
+  float2 wc[NK];
+#pragma unroll
+  for (int k = 0; k < NK; k++) {
+    if (MODE == 0) {
+      wc[k] = W[k * w_cols + j];
+    } else {
+      wc[k] = W[j * w_cols + k];
+      wc[k].y = -wc[k].y;
+    }
+  }
+  for (long long row0 = (long long)blockIdx.x * kTileRows; row0 < rows; row0 += (long long)gridDim.x * kTileRows) {
+    const int nr = (int)min((long long)kTileRows, rows - row0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < nr * NK; e += blockDim.x) xs[e] = __ldcs(x + row0 * NK + e);
+    __syncthreads();
+    for (int row = rg; row < nr; row += nrg) {
+      const float4* xr = reinterpret_cast<const float4*>(xs + row * NK);
+      float sr = 0.f, si = 0.f, tr = 0.f, ti = 0.f;
+#pragma unroll
+      for (int k = 0; k < NK / 2; k++) {
+        const float4 a = xr[k];
+        sr = fmaf(a.x, wc[2 * k].x, sr); sr = fmaf(-a.y, wc[2 * k].y, sr);
+        si = fmaf(a.x, wc[2 * k].y, si); si = fmaf(a.y, wc[2 * k].x, si);
+        tr = fmaf(a.z, wc[2 * k + 1].x, tr); tr = fmaf(-a.w, wc[2 * k + 1].y, tr);
+        ti = fmaf(a.z, wc[2 * k + 1].y, ti); ti = fmaf(a.w, wc[2 * k + 1].x, ti);
+      }
+      __stcs(r + (row0 + row) * nj + j, make_float2(sr + tr, si + ti));
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) mix_back_w_kernel(float* __restrict__ Wg, const float2* __restrict__ x,
                                                          const float2* __restrict__ g, long long rows, int ni, int nj,
                                                          long long rows_per_block) {
@@ -82,8 +121,11 @@ __global__ void __launch_bounds__(256) mix_back_w_kernel(float* __restrict__ Wg,
       if (pair < npairs) {
         const int i = pair / nj, j = pair - i * nj;
         float sr = accr[p], si = acci[p];
+        const float2* xa = xs + i;
+        const float2* gb = gs + j;
+#pragma unroll 8
         for (int row = 0; row < nr; row++) {  // conj(x) g
-          const float2 a = xs[row * ni + i], b = gs[row * nj + j];
+          const float2 a = xa[row * ni], b = gb[row * nj];
           sr = fmaf(a.x, b.x, sr); sr = fmaf(a.y, b.y, sr);
           si = fmaf(a.x, b.y, si); si = fmaf(-a.y, b.x, si);
         }
@@ -112,7 +154,17 @@ int launch_mix(float* r, const float* x, const float* W, long long rows, int n_i
   const size_t smem = ((size_t)nk * (nj + 1) + (size_t)kTileRows * nk) * sizeof(float2);
   const unsigned blocks = (unsigned)std::min<long long>((rows + kTileRows - 1) / kTileRows, 148LL * 16);
   cudaError_t e;
-  if (mode == 0) {
+  const bool pow2 = (nj & (nj - 1)) == 0 && nj <= 32;
+  if (pow2 && (nk == 16 || nk == 32)) {
+    const size_t smem_r = (size_t)kTileRows * nk * sizeof(float2);
+    float2* rp = reinterpret_cast<float2*>(r);
+    const float2 *xp = reinterpret_cast<const float2*>(x), *wp = reinterpret_cast<const float2*>(W);
+    if (mode == 0 && nk == 16) mix_reg_kernel<0, 16><<<blocks, 256, smem_r, s>>>(rp, xp, wp, rows, nj, n_out);
+    else if (mode == 0) mix_reg_kernel<0, 32><<<blocks, 256, smem_r, s>>>(rp, xp, wp, rows, nj, n_out);
+    else if (nk == 16) mix_reg_kernel<1, 16><<<blocks, 256, smem_r, s>>>(rp, xp, wp, rows, nj, n_out);
+    else mix_reg_kernel<1, 32><<<blocks, 256, smem_r, s>>>(rp, xp, wp, rows, nj, n_out);
+    e = cudaSuccess;
+  } else if (mode == 0) {
     e = cudaFuncSetAttribute(mix_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess)
       mix_kernel<0><<<blocks, 256, smem, s>>>(reinterpret_cast<float2*>(r), reinterpret_cast<const float2*>(x),
