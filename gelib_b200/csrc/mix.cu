@@ -7,9 +7,11 @@
 // rows = every (cell, m) of the part; all arrays dense complex64.  In GElib this is torch.matmul per part
 // (python/src/gelib/SO3vec.py:174-177, python/src/gelib/SO3weights.py:22-85); with 16 channels the library GEMM runs at
 // a tenth of the memory rate, and the mixing of config 5's pipeline cost as much as a fifth of its product.  The
-// kernels here are bound by memory: a block stages a tile of rows (and the matrix) in shared memory with coalesced
-// loads and every thread forms one output element per pass; the weight gradient keeps one (i,j) sum per thread over
+// kernels here are bound by memory: a block stages tiles of rows (and the matrix) in shared memory with coalesced
+// asynchronous copies, one tile in flight while the other is worked on, and every thread forms one output element per pass; the weight gradient keeps one (i,j) sum per thread over
 // the block's rows and adds it to global memory once.
+#include <cuda_pipeline.h>
+
 #include <algorithm>
 
 #include "plan.h"
@@ -20,6 +22,11 @@ namespace {
 
 constexpr int kMixMaxN = 64;   // channels on either side
 constexpr int kTileRows = 64;  // rows per block and pass
+
+// `count` complex numbers from global to shared memory, asynchronously (8 bytes per copy; the caller commits).
+__device__ __forceinline__ void tile_copy_async(float2* dst, const float2* src, int count) {
+  for (int e = threadIdx.x; e < count; e += blockDim.x) __pipeline_memcpy_async(dst + e, src + e, 8);
+}
 
 template <int MODE>
 __global__ void __launch_bounds__(256) mix_kernel(float2* __restrict__ r, const float2* __restrict__ x, const float2* __restrict__ W,
@@ -63,8 +70,7 @@ __global__ void __launch_bounds__(256) mix_kernel(float2* __restrict__ r, const 
 template <int MODE, int NK>
 __global__ void __launch_bounds__(256) mix_reg_kernel(float2* __restrict__ r, const float2* __restrict__ x,
                                                       const float2* __restrict__ W, long long rows, int nj, int w_cols) {
-  extern __shared__ float2 sm[];
-  float2* xs = sm;  // [kTileRows][NK]
+  extern __shared__ float2 sm[];  // two tiles [kTileRows][NK]: one is loaded while the other is worked on
   const int j = threadIdx.x % nj, rg = threadIdx.x / nj, nrg = blockDim.x / nj;
   float2 wc[NK];
 #pragma unroll
@@ -76,11 +82,18 @@ __global__ void __launch_bounds__(256) mix_reg_kernel(float2* __restrict__ r, co
       wc[k].y = -wc[k].y;
     }
   }
-  for (long long row0 = (long long)blockIdx.x * kTileRows; row0 < rows; row0 += (long long)gridDim.x * kTileRows) {
+  const long long stride = (long long)gridDim.x * kTileRows;
+  long long row0 = (long long)blockIdx.x * kTileRows;
+  if (row0 < rows) tile_copy_async(sm, x + row0 * NK, (int)min((long long)kTileRows, rows - row0) * NK);
+  __pipeline_commit();
+  for (int buf = 0; row0 < rows; row0 += stride, buf ^= 1) {
     const int nr = (int)min((long long)kTileRows, rows - row0);
+    const long long next = row0 + stride;
+    if (next < rows) tile_copy_async(sm + (buf ^ 1) * kTileRows * NK, x + next * NK, (int)min((long long)kTileRows, rows - next) * NK);
+    __pipeline_commit();
+    __pipeline_wait_prior(1);
     __syncthreads();
-    for (int e = threadIdx.x; e < nr * NK; e += blockDim.x) xs[e] = __ldcs(x + row0 * NK + e);
-    __syncthreads();
+    const float2* xs = sm + buf * kTileRows * NK;
     for (int row = rg; row < nr; row += nrg) {
       const float4* xr = reinterpret_cast<const float4*>(xs + row * NK);
       float sr = 0.f, si = 0.f, tr = 0.f, ti = 0.f;
@@ -94,27 +107,37 @@ __global__ void __launch_bounds__(256) mix_reg_kernel(float2* __restrict__ r, co
       }
       __stcs(r + (row0 + row) * nj + j, make_float2(sr + tr, si + ti));
     }
+    __syncthreads();  // the tile may be overwritten by the copy after next
   }
 }
 
 __global__ void __launch_bounds__(256) mix_back_w_kernel(float* __restrict__ Wg, const float2* __restrict__ x,
                                                          const float2* __restrict__ g, long long rows, int ni, int nj,
                                                          long long rows_per_block) {
-  extern __shared__ float2 sm[];
-  float2* xs = sm;                    // [kTileRows][ni]
-  float2* gs = sm + kTileRows * ni;   // [kTileRows][nj]
+  extern __shared__ float2 sm[];      // two pairs of tiles [kTileRows][ni], [kTileRows][nj]
+  const int tile = kTileRows * (ni + nj);
   const long long begin = (long long)blockIdx.x * rows_per_block, end = min(rows, begin + rows_per_block);
   constexpr int kPairs = (kMixMaxN * kMixMaxN + 255) / 256;  // (i,j) sums per thread
   float accr[kPairs], acci[kPairs];
 #pragma unroll
   for (int p = 0; p < kPairs; p++) accr[p] = acci[p] = 0.f;
   const int npairs = ni * nj;
-  for (long long row0 = begin; row0 < end; row0 += kTileRows) {
+  auto copy_tile = [&](int buf, long long row0) {
     const int nr = (int)min((long long)kTileRows, end - row0);
+    tile_copy_async(sm + buf * tile, x + row0 * ni, nr * ni);
+    tile_copy_async(sm + buf * tile + kTileRows * ni, g + row0 * nj, nr * nj);
+  };
+  if (begin < end) copy_tile(0, begin);
+  __pipeline_commit();
+  int buf = 0;
+  for (long long row0 = begin; row0 < end; row0 += kTileRows, buf ^= 1) {
+    const int nr = (int)min((long long)kTileRows, end - row0);
+    if (row0 + kTileRows < end) copy_tile(buf ^ 1, row0 + kTileRows);
+    __pipeline_commit();
+    __pipeline_wait_prior(1);
     __syncthreads();
-    for (int e = threadIdx.x; e < nr * ni; e += blockDim.x) xs[e] = __ldcs(x + row0 * ni + e);
-    for (int e = threadIdx.x; e < nr * nj; e += blockDim.x) gs[e] = __ldcs(g + row0 * nj + e);
-    __syncthreads();
+    const float2* xs = sm + buf * tile;
+    const float2* gs = xs + kTileRows * ni;
 #pragma unroll
     for (int p = 0; p < kPairs; p++) {
       const int pair = threadIdx.x + 256 * p;
@@ -133,6 +156,7 @@ __global__ void __launch_bounds__(256) mix_back_w_kernel(float* __restrict__ Wg,
         acci[p] = si;
       }
     }
+    __syncthreads();  // the tiles may be overwritten by the copy after next
   }
 #pragma unroll
   for (int p = 0; p < kPairs; p++) {
@@ -156,7 +180,7 @@ int launch_mix(float* r, const float* x, const float* W, long long rows, int n_i
   cudaError_t e;
   const bool pow2 = (nj & (nj - 1)) == 0 && nj <= 32;
   if (pow2 && (nk == 16 || nk == 32)) {
-    const size_t smem_r = (size_t)kTileRows * nk * sizeof(float2);
+    const size_t smem_r = (size_t)2 * kTileRows * nk * sizeof(float2);
     float2* rp = reinterpret_cast<float2*>(r);
     const float2 *xp = reinterpret_cast<const float2*>(x), *wp = reinterpret_cast<const float2*>(W);
     if (mode == 0 && nk == 16) mix_reg_kernel<0, 16><<<blocks, 256, smem_r, s>>>(rp, xp, wp, rows, nj, n_out);
@@ -189,7 +213,7 @@ int launch_mix_back_w(float* Wg, const float* x, const float* g, long long rows,
   long long rpb = (rows + want_blocks - 1) / want_blocks;
   rpb = (rpb + kTileRows - 1) / kTileRows * kTileRows;
   const unsigned blocks = (unsigned)((rows + rpb - 1) / rpb);
-  const size_t smem = (size_t)kTileRows * (n_in + n_out) * sizeof(float2);
+  const size_t smem = (size_t)2 * kTileRows * (n_in + n_out) * sizeof(float2);
   cudaError_t e = cudaFuncSetAttribute(mix_back_w_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e == cudaSuccess)
     mix_back_w_kernel<<<blocks, 256, smem, s>>>(Wg, reinterpret_cast<const float2*>(x), reinterpret_cast<const float2*>(g), rows,
