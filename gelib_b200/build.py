@@ -15,7 +15,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libgelib_b200.so")
 SOURCES = ["bank.cu", "plan.cu", "cg_fwd.cu", "cg_fwd_tc.cu", "cg_bwd.cu", "cg_bwd_pair.cu", "cg_bwd_tc.cu", "cg_narrow.cu", "cg_narrow1_bwd.cu", "cg_strided.cu", "diag.cu", "diag_fwd.cu", "diag_bwd.cu", "spharm.cu", "probe.cu", "gather_apply.cu", "mix.cu", "cabi.cu"]
-HEADERS = ["common.h", "plan.h", "tc_common.h", os.path.join("..", "..", "include", "gelib_b200.h")]
+HEADERS = ["common.h", "plan.h", "tc_common.h", "tma_maps.h", os.path.join("..", "..", "include", "gelib_b200.h")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-Xcompiler", "-fPIC",
          "--expt-relaxed-constexpr"] + os.environ.get("GELIB_NVCC_FLAGS", "").split()

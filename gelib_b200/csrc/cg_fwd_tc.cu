@@ -28,6 +28,7 @@
 
 #include "plan.h"
 #include "tc_common.h"
+#include "tma_maps.h"
 
 namespace gelib_b200 {
 
@@ -60,7 +61,19 @@ struct FwdTcArgs {
   int offs_extra;
   int* status;
   int drop_commit;  // test hook: the MMAs are issued but never committed, so every wait of the kernel runs out
+  // Output tiles leave through tensor maps (one per r part: every y part has the same channel count N2 then):
+  // two tensor stores per slab from a swizzled staging block instead of one 256-byte bulk store per lane and row.
+  int use_tma;
+  unsigned tk[kMaxParts][6];  // (outer, inner) cell coordinate of the maps = (b, g0, g1) x these multipliers
 };
+
+// One tensor store: 32 rows x 128 bytes of a slab (rank-5 map; the box is 32 x 32 x 1 x 1 x 1 floats).
+__device__ __forceinline__ void tma_store_5d(const void* map, uint32_t src, int c0, int c1, int c2, int c3, int c4) {
+  asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+               : "memory");
+}
 
 struct Slab {
   int4 r;
@@ -135,8 +148,9 @@ __device__ __forceinline__ void load_slab(const FwdTcArgs& A, int g, int q, int 
 
 // ---- the kernel ------------------------------------------------------------------------------------------------
 
-__global__ void __launch_bounds__(kThreads, 1) cg_fwd_tc_kernel(const __grid_constant__ FwdTcArgs A) {
-  extern __shared__ __align__(128) unsigned char sm[];
+__global__ void __launch_bounds__(kThreads, 1) cg_fwd_tc_kernel(const __grid_constant__ FwdTcArgs A,
+                                                                const __grid_constant__ TmaMaps M) {
+  extern __shared__ __align__(1024) unsigned char sm[];
   uint64_t* mdone = reinterpret_cast<uint64_t*>(sm);  // [4] MMAs of a set's group complete (tcgen05.commit)
   int* ev = reinterpret_cast<int*>(sm + 32);          // [4] arrivals of the set's warps that have stored their A rows
   uint32_t* tbase_s = reinterpret_cast<uint32_t*>(sm + 48);
@@ -145,7 +159,9 @@ __global__ void __launch_bounds__(kThreads, 1) cg_fwd_tc_kernel(const __grid_con
   long long* rsm = reinterpret_cast<long long*>(rptr + kMaxParts);           // output row stride
   unsigned char* bt = sm + kHeaderBytes;
   float* xs = reinterpret_cast<float*>(bt + A.bt_bytes);
-  unsigned char* stage = reinterpret_cast<unsigned char*>(xs + A.x_floats);  // 32 rows of kStagePitch per warp
+  // per warp 32 rows of kStagePitch, or (tensor stores) two swizzled half-slabs of 4096 bytes; the block starts at a
+  // multiple of 1024 bytes of the shared-memory ADDRESS (the swizzle pattern is a function of the address)
+  const uint32_t stage_base = (smem_u32(sm) + kHeaderBytes + A.bt_bytes + 4 * A.x_floats + 1023u) & ~1023u;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long cell = blockIdx.x;
@@ -182,7 +198,10 @@ __global__ void __launch_bounds__(kThreads, 1) cg_fwd_tc_kernel(const __grid_con
     // tensor-memory columns of set s: A hi 32, A lo 32, accumulator 64
     const uint32_t tA = tbase + 128 * s + lanes, tD = tA + 64;
     const uint32_t bt_u32 = smem_u32(bt), xs_u32 = smem_u32(xs) + 8 * lane;
-    const uint32_t stage_u32 = smem_u32(stage) + warp * (32 * kStagePitch);
+    const uint32_t stage_u32 = stage_base + warp * (A.use_tma ? 8192 : 32 * kStagePitch);
+    // cell coordinates of the tensor maps
+    const unsigned cg1 = (unsigned)cell % (unsigned)A.cg.G1, ct = (unsigned)cell / (unsigned)A.cg.G1;
+    const unsigned cg0 = ct % (unsigned)A.cg.G0, cb = ct / (unsigned)A.cg.G0;
     const int ngs = (A.ngroups - s + 3) >> 2;
     uint32_t par = 0;
     bool ok = true;
@@ -260,19 +279,46 @@ __global__ void __launch_bounds__(kThreads, 1) cg_fwd_tc_kernel(const __grid_con
       if (cur.valid()) {
         // Each lane puts its 256-byte output row into the warp's staging block (272-byte pitch: conflict-free) and
         // hands it to the bulk-copy engine: the store stream runs on its own, off the warp's critical path.
-        bulk_wait_read();  // the previous slab's rows have left the staging block
+        if (A.use_tma) {
+          // Lane = output row n1: its 16-byte chunk c of half hlf goes to chunk c ^ (n1 & 7) of row n1 of that half
+          // (the 128-byte swizzle of the tensor map: conflict-free here, undone by the copy engine); lane 0 then
+          // hands the two half-slabs to the copy engine with one tensor store each.
+          if (lane == 0) bulk_wait_read();  // the previous slab has left the staging block (lane 0 issued its stores)
+          __syncwarp();
 #pragma unroll
-        for (int hlf = 0; hlf < 2; hlf++) {
-          uint32_t d[32];
-          tmem_ld32(tD + 32 * hlf, d);
+          for (int hlf = 0; hlf < 2; hlf++) {
+            uint32_t d[32];
+            tmem_ld32(tD + 32 * hlf, d);
 #pragma unroll
-          for (int i = 0; i < 8; i++)
-            sts128(stage_u32 + lane * kStagePitch + 128 * hlf + 16 * i, d[4 * i], d[4 * i + 1], d[4 * i + 2], d[4 * i + 3]);
+            for (int i = 0; i < 8; i++)
+              sts128(stage_u32 + 4096 * hlf + lane * 128 + ((i ^ (lane & 7)) << 4), d[4 * i], d[4 * i + 1], d[4 * i + 2], d[4 * i + 3]);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the rows are read by the async proxy
+          __syncwarp();
+          if (lane == 0) {
+            const int ri = cur.ri(), n2t = cur.n2tot();
+            const int c1 = cur.r.z / n2t, col = 2 * (cur.r.z - c1 * n2t);
+            const int ca = (int)(cb * A.tk[ri][0] + cg0 * A.tk[ri][1] + cg1 * A.tk[ri][2]);
+            const int cc = (int)(cb * A.tk[ri][3] + cg0 * A.tk[ri][4] + cg1 * A.tk[ri][5]);
+            tma_store_5d(&M.m[ri], stage_u32, col, c1, cur.row(), cc, ca);
+            tma_store_5d(&M.m[ri], stage_u32 + 4096, col + 32, c1, cur.row(), cc, ca);
+            bulk_commit();
+          }
+        } else {
+          bulk_wait_read();  // the previous slab's rows have left the staging block
+#pragma unroll
+          for (int hlf = 0; hlf < 2; hlf++) {
+            uint32_t d[32];
+            tmem_ld32(tD + 32 * hlf, d);
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+              sts128(stage_u32 + lane * kStagePitch + 128 * hlf + 16 * i, d[4 * i], d[4 * i + 1], d[4 * i + 2], d[4 * i + 3]);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the rows are read by the async proxy
+          float* dst = rptr[cur.ri()] + (long long)cur.row() * rsm[cur.ri()] + 2LL * cur.r.z + 2LL * lane * cur.n2tot();
+          bulk_store(dst, stage_u32 + lane * kStagePitch, 256);
+          bulk_commit();
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the rows are read by the async proxy
-        float* dst = rptr[cur.ri()] + (long long)cur.row() * rsm[cur.ri()] + 2LL * cur.r.z + 2LL * lane * cur.n2tot();
-        bulk_store(dst, stage_u32 + lane * kStagePitch, 256);
-        bulk_commit();
       }
       tc_fence_before();  // the reads of the accumulator precede the next group's arrival
     }
@@ -339,8 +385,8 @@ int launch_cg_fwd_tc(const VecCall& c, cudaStream_t s, int min_slabs) {
   a.nr = (int)c.r.size();
   a.bt_bytes = round_up(bt, 128);
   a.x_floats = round_up(xf, 32);
-  const size_t smem = (size_t)kHeaderBytes + a.bt_bytes + 4 * (size_t)a.x_floats + (size_t)kWarps * 32 * kStagePitch;
-  if (smem > 227 * 1024) return -1;
+  const size_t front = ((size_t)kHeaderBytes + a.bt_bytes + 4 * (size_t)a.x_floats + 1023) & ~(size_t)1023;
+  if (front + 1024 + (size_t)kWarps * 32 * kStagePitch > 227 * 1024) return -1;
 
   std::vector<int> key = {8 /*family*/, (int)c.x.size(), (int)c.y.size(), (int)c.r.size()};
   for (const auto& p : c.x) { key.push_back(p.l); key.push_back(p.n); }
@@ -397,9 +443,28 @@ int launch_cg_fwd_tc(const VecCall& c, cudaStream_t s, int min_slabs) {
   // option "inject_timeout" (tests only): exercise the bounded waits and the status word without any fault
   a.drop_commit = inject_timeout();
   a.status = status;  // unified addressing: the host pointer of mapped memory is valid on the device
+  // tensor stores when every y part has the same channel count (the rows of an r part are then a matrix with rows of
+  // N2 channels in which every tile is 32 consecutive rows) and the views fit rank-5 maps
+  TmaMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  a.use_tma = 0;
+  if (pair_tma() && c.offs_extra == 0) {
+    bool uniform = true;
+    for (const auto& p : c.y) uniform = uniform && p.n == c.y[0].n;
+    if (uniform) {
+      std::vector<int> info;
+      for (size_t i = 0; i < c.r.size(); i++) {
+        info.push_back((int)i);
+        info.push_back(c.y[0].n);
+        info.push_back((c.r[i].n + c.y[0].n - 1) / c.y[0].n);
+      }
+      if (encode_part_maps(c.r, c.cg, 0, (int)c.r.size(), info.data(), a.tk, maps)) a.use_tma = 1;
+    }
+  }
+  const size_t smem = front + 1024 + (size_t)kWarps * (a.use_tma ? 8192 : 32 * kStagePitch);
   cudaError_t e = cudaFuncSetAttribute(cg_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e == cudaSuccess) {
-    cg_fwd_tc_kernel<<<(unsigned)c.cg.ncells, kThreads, smem, s>>>(a);
+    cg_fwd_tc_kernel<<<(unsigned)c.cg.ncells, kThreads, smem, s>>>(a, maps);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) return check_cuda(e, fn, "tensor-core forward kernel launch");
