@@ -231,7 +231,8 @@ double gelib_probe_fp32_tflops(float* scratch, int ctas, int reps, void* stream)
  * here the choice can be pinned.  name "fwd": "auto" | "simt" | "tcgen05" | "tcgen05!";  name "bwd": "auto" |
  * "simt" | "pair" | "pair!" | "tcgen05" | "tcgen05!" (a trailing "!" refuses calls the named kernel cannot take
  * instead of falling back);  name "pair_tma": "1" | "0" (the pair backward kernel fills its ring with tensor copies
- * when the views of g fit rank-5 tensor maps, "0": always with cp.async);  name "narrow1": "1" | "0" (the
+ * and the tensor-core forward stores its tiles with tensor copies when the views fit rank-5 tensor maps, "0": cp.async
+ * and per-row bulk copies instead);  name "narrow1": "1" | "0" (the
  * gradient of y for a one-channel x takes the kernel written for that shape, "0": the general narrow kernel);
  * name "inject_timeout": "0" | "1" (tests:
  * one bounded device wait is made to run out).
