@@ -422,6 +422,18 @@ def test_pair_backward_on_grids(G, oracle, opt, copies, layout):
     xg = [torch.zeros(B, G0, G1, 2 * l + 1, n, dtype=torch.complex64, device="cuda") for l, n in tau_x.items()]
     yg = [torch.zeros(B, G0, G1, 2 * l + 1, n, dtype=torch.complex64, device="cuda") for l, n in tau_y.items()]
     V = G.backend.SO3vec.view
+    # the tensor-core forward on the same grid: its output tiles leave through tensor stores when the views allow
+    # (here y has two channel counts, so only a uniform sub-vector takes them) -- values against the oracle either way
+    opt("fwd", "tcgen05!")
+    for ty in (tau_y, {1: 32}):
+        tr = oracle.cg_type(tau_x, ty, 3, False)
+        want = {l: np.zeros((B * G0 * G1, 2 * l + 1, n), np.complex64) for l, n in tr.items()}
+        oracle.vec_cg(want, {l: flat(t) for l, t in x.items()}, {l: flat(y[l]) for l in ty}, False)
+        rfull = {l: grid(560 + l, l, n) for l, n in tr.items()}  # garbage to overwrite, same layout as the inputs
+        assert V(list(rfull.values())).addCGproduct(V(list(x.values())), V([y[l] for l in ty]), overwrite=True)
+        torch.cuda.synchronize()
+        for l, w in want.items():
+            assert rel_err(flat(rfull[l]), w) < TOL_BIG
     assert G.backend.SO3vec.addCGproduct_back01(V(xg), V(yg), V(list(g.values())), V(list(x.values())), V(list(y.values())))
     torch.cuda.synchronize()
     for p, w in zip(xg, xg_w.values()):
@@ -431,8 +443,11 @@ def test_pair_backward_on_grids(G, oracle, opt, copies, layout):
 
 
 @pytest.mark.parametrize("B,tau_x,tau_y,maxl,tol", TC_CASES)
-@pytest.mark.parametrize("kernel", ["tcgen05!", "simt", "auto"])
+@pytest.mark.parametrize("kernel", ["tcgen05!", "tcgen05! bulk stores", "simt", "auto"])
 def test_vec_forward_named_kernel(G, oracle, opt, B, tau_x, tau_y, maxl, tol, kernel):
+    if kernel.endswith("bulk stores"):  # the tensor-core forward without tensor stores (per-row bulk copies)
+        opt("pair_tma", "0")
+        kernel = "tcgen05!"
     opt("fwd", kernel)  # "tcgen05!": fail instead of falling back to the SIMT kernel
     x, y = _vec_inputs(tau_x, tau_y, B, 60)
     tau_r = oracle.cg_type(tau_x, tau_y, maxl, False)
