@@ -219,14 +219,19 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 int launch_cg_fwd(const VecCall& c, cudaStream_t s) {
   static const char* fn = "SO3vec_addCGproduct";
   // Calls that qualify (channel counts that are multiples of 32, output overwritten) and have at least 512 slabs
-  // (rows of 32 x 32 channel tiles) per cell go to the tensor-core kernel of cg_fwd_tc.cu: with fewer its fixed
+  // (rows of 32 x 32 channel tiles) per cell -- 240 when it can use tensor stores -- go to the tensor-core kernel of
+  // cg_fwd_tc.cu: with fewer its fixed
   // cost per cell (staging the y tables, tensor-memory allocation) outweighs its cheaper slabs.
   // Option "fwd" (initially GELIB_B200_FWD): "simt" keeps everything on this file's kernel, "tcgen05" sends
   // everything that qualifies there, "tcgen05!" also refuses calls that do not qualify (tests use it to be sure which
   // kernel ran).
   const int mode = fwd_mode();
   if (mode != kFwdSimt) {
-    const int rc = launch_cg_fwd_tc(c, s, mode == kFwdAuto ? 512 : 0);
+    // with tensor stores (every y part the same channel count) the crossover measured is lower: 252 slabs per cell
+    // (l1 = 3 x l2 = 4, 64 channels) 1.36 against 1.59 ms, 375 (maxl 4 x 32) a tie, 204 (maxl 2 x 64) 2.35 against 2.14
+    bool uniform = pair_tma() && c.offs_extra == 0 && !c.y.empty();
+    for (const auto& p : c.y) uniform = uniform && p.n == c.y[0].n;
+    const int rc = launch_cg_fwd_tc(c, s, mode == kFwdAuto ? (uniform ? 240 : 512) : 0);
     if (rc != -1) return rc;
     if (mode == kFwdTcStrict) return fail(GELIB_INVALID, fn, "the call does not qualify for the tcgen05 kernel");
   }
