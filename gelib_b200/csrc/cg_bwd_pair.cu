@@ -665,11 +665,21 @@ int launch_cg_bwd_pair(const VecCall& c, cudaStream_t s, int min_groups) {
       p.h_jobs[3 + 3 * kv.second] = kv.first.second;
       p.h_jobs[4 + 3 * kv.second] = slot_rows[kv.second];
     }
+    long long entries = 0;  // band entries of all groups: the last word of the list
+    for (size_t g = 0; g < p.h_items.size(); g += kRec) entries += (p.h_items[g].x >> 8) & 0xff;
+    p.h_jobs.push_back((int)std::min<long long>(entries, 0x7fffffffLL));
   });
   if (!plan) return GELIB_CUDA_ERROR;
   if (plan->nitems == 0 || c.cg.ncells == 0) return GELIB_OK;
   // a cell with only a few groups does not fill the pipeline of 12 warps: the one-slab-per-warp kernel is faster there
-  if (min_groups > 0 && plan->nitems / kRec < min_groups) return -1;
+  // Automatic choice: the kernel pays a fixed cost per group (handshake, slab loads into registers) that short bands
+  // do not repay.  Measured against the kernel of cg_bwd.cu at 32 channels: maxl 4 (188 groups, 3.1 entries per
+  // group) 7.98 against 8.15 ms, maxl 3 (92 groups, 2.5 entries per group) 7.37 against 6.25, maxl 2 6.12 against 4.08;
+  // at 64 channels maxl 3 (368 groups, 2.5 entries per group) 3.46 against 2.91.
+  if (min_groups > 0) {
+    const long long ng = plan->nitems / kRec, entries = plan->h_jobs.empty() ? 0 : plan->h_jobs.back();
+    if (ng < min_groups || entries < 3 * ng) return -1;
+  }
 
   a.cg = c.cg;
   a.recs = plan->items;
