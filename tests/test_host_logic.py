@@ -215,10 +215,11 @@ def test_reference_python_package_imports_on_gelib_base():
     import subprocess
     import sys
     import pytest
-    ref = "/root/reference/python/src"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    # the GElib checkout: GELIB_REFERENCE_SRC, or a directory "reference" beside this repository
+    ref = os.environ.get("GELIB_REFERENCE_SRC", os.path.join(os.path.dirname(root), "reference", "python", "src"))
     if not os.path.isdir(os.path.join(ref, "gelib")):
         pytest.skip("the GElib source tree is not present")
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     code = (
         "import torch, gelib, gelib_base\n"
         "assert gelib_base.SO3part.view.__module__ == 'gelib_b200.backend'\n"
